@@ -2,6 +2,7 @@
 from .fusitar import FusitarConfig
 from .gemma2 import ConfigError, Gemma2Config
 from .kofutar import KofutarConfig
+from .teluzen import TeluzenConfig
 from .registry import (
     architectures,
     config_class_for,
@@ -21,11 +22,13 @@ from .spec import (
     HeadSpec,
     InputMixSpec,
     LatentAttentionSpec,
+    MLPSpec,
     MLSTMSpec,
     ModelSpec,
     MoESpec,
     NormSpec,
     PositionSpec,
+    RopeScaling,
     ScheduleEntry,
     default_schedule,
 )

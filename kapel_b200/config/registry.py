@@ -15,6 +15,7 @@ from typing import Dict, Tuple
 from .fusitar import FusitarConfig
 from .gemma2 import ConfigError, Gemma2Config
 from .kofutar import KofutarConfig
+from .teluzen import TeluzenConfig
 
 _ARCHITECTURES: Dict[str, type] = {}
 
@@ -100,3 +101,4 @@ def read_config_file(name_or_path) -> dict:
 register_architecture(Gemma2Config, Gemma2Config.architecture, Gemma2Config.model_type)
 register_architecture(FusitarConfig, FusitarConfig.architecture, FusitarConfig.model_type)
 register_architecture(KofutarConfig, KofutarConfig.architecture, KofutarConfig.model_type)
+register_architecture(TeluzenConfig, TeluzenConfig.architecture, TeluzenConfig.model_type)

@@ -27,15 +27,31 @@ class NormSpec:
 
 
 @dataclass(frozen=True)
+class RopeScaling:
+    """Frequencies stretched by wavelength: with r rotated components and base theta, the pair that
+    turns t times over `original` positions is number n(t) = r ln(original / (2 pi t)) / (2 ln theta);
+    lo = max(floor(n(fast)), 0), hi = min(ceil(n(slow)), r - 1), ramp_j = clamp((j - lo) / max(hi - lo,
+    0.001), 0, 1); pair j turns at f_j / factor * ramp_j + f_j (1 - ramp_j), and cos and sin are both
+    multiplied by 0.1 ln(factor) + 1."""
+
+    factor: float
+    original: float
+    fast: float
+    slow: float
+
+
+@dataclass(frozen=True)
 class PositionSpec:
-    """kind "rope": rotation of the first `rotary_dim` components, pairing "half" (j, j+r/2), by the
-    angle position * theta^(-2j/r) / `divisor` (a divisor above 1 stretches the positions)."""
+    """kind "rope": rotation of the first `rotary_dim` components, pairing "half" (j, j+r/2) or
+    "neighbours" (2j, 2j+1), by the angle position * theta^(-2j/r) / `divisor` (a divisor above 1
+    stretches the positions); with `scaling` the frequencies follow `RopeScaling` instead."""
 
     kind: str = "rope"
     theta: float = 10000.0
     rotary_dim: int = 0
     pairing: str = "half"
     divisor: float = 1.0
+    scaling: Optional[RopeScaling] = None
 
 
 @dataclass(frozen=True)
@@ -50,6 +66,17 @@ class AttentionSpec:
     a norm over the whole projection (all heads' rows at once) ahead of the split into heads.
     `q_head_norm` / `k_head_norm`: an RMS norm over each head's vector with one weight of the head's
     size for all heads, ahead of the rotation.
+
+    `bias`: q, k and v have biases (roles q_bias, k_bias, v_bias). `pool` P > 0 (with a window): beside
+    the window's tokens a query sees one key and value for every block of P positions that lies wholly
+    below its window, the means of the block's keys and values as the cache holds them, in the same
+    softmax; `pool_blocks` is the most blocks a request can have (its position limit / P). `head_temp`:
+    a head's scores are multiplied by its number of role temp [heads]. `talk`: after the softmax the
+    heads' weights are mixed, w'_h = sum_g talk[h, g] w_g (role talk [heads, heads]), and head h applies
+    w'_h to the values of its own kv head. `value_mix` "source": this layer's values (of this step's
+    rows, before they are cached) are kept for later layers; "mix": v <- (1 - l) v + l v_source with l
+    the one value of role vmix, and the mixed v is what is cached; the layers of one `value_mix_key`
+    share a source.
     """
 
     hidden: int
@@ -69,6 +96,13 @@ class AttentionSpec:
     gated: bool = False
     q_head_norm: Optional[NormSpec] = None
     k_head_norm: Optional[NormSpec] = None
+    bias: bool = False
+    pool: int = 0
+    pool_blocks: int = 0
+    head_temp: bool = False
+    talk: bool = False
+    value_mix: Optional[str] = None
+    value_mix_key: str = "values"
 
 
 @dataclass(frozen=True)
@@ -152,7 +186,10 @@ class MoESpec:
     """A mixture of small feed-forwards: down(act(up(h))) for the `top` experts a token chooses,
     added up with the router's weights.
 
-    Router scores s = `scoring`(router(h)); experts are chosen by s + the tensor `correction`
+    Router scores s = `scoring`(router(h)) ("sigmoid", "softmax" over all experts, or "softmax_chosen":
+    the logits choose and the chosen experts are weighted by the softmax over their logits alone);
+    with `gated` an expert is down(act(gate(h)) * up(h)) (pattern `gate`); `shared`: the spec of a
+    feed-forward that every token runs and whose output is added. Experts are chosen by s + the tensor `correction`
     (where one is named) but weighted by s; with `groups` > 1 the experts form that many equal
     groups of neighbours, a group scores the sum of its `group_top` best choice scores, and only
     experts of the best `keep_groups` groups can be chosen; `renormalize` divides the chosen
@@ -171,6 +208,8 @@ class MoESpec:
     group_top: int = 2
     scoring: str = "sigmoid"
     renormalize: bool = False
+    gated: bool = False
+    shared: Optional[object] = None
     kind: str = "moe"
 
 
@@ -183,6 +222,17 @@ class GatedMLPSpec:
     activation: str
     weights: Mapping[str, str]       # roles gate, up, down
     kind: str = "gated_mlp"
+
+
+@dataclass(frozen=True)
+class MLPSpec:
+    """down(act(up(h))); `activation` is "relu2" (the square of relu), "gelu_tanh" or "silu"."""
+
+    hidden: int
+    intermediate: int
+    activation: str
+    weights: Mapping[str, str]       # roles up, down
+    kind: str = "mlp"
 
 
 @dataclass(frozen=True)
@@ -231,10 +281,15 @@ class InputMixSpec:
 
 @dataclass(frozen=True)
 class EmbedSpec:
+    """x = table[token] * scale; with `positions` (a tensor [max_positions, hidden]) plus that table's
+    row of the token's position, not scaled."""
+
     weight: str
     scale: float                     # exact; rounded to the activation dtype when `round_scale`
     round_scale: bool = True
     kind: str = "embedding"
+    positions: Optional[str] = None
+    max_positions: int = 0
 
 
 @dataclass(frozen=True)

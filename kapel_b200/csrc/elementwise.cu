@@ -13,9 +13,12 @@ KB_TIMELINE_ARRAY(elementwise) // slots: kind 3 rotation and append (rows, slice
 
 // ---------------------------------------------------------------------------------------
 // x[r, :] = table[ids[r], :] * scale, in 32-bit. An id outside the table gives a row of NaN.
+// With a table of learned positions, its row positions[r] is added (not scaled); a position outside
+// that table (a row of no token) adds nothing.
 template <typename T>
 __global__ void embed_kernel(float* __restrict__ out, const T* __restrict__ table, const int* __restrict__ ids,
-                             int rows, int width, int vocab, float scale) {
+                             int rows, int width, int vocab, float scale, const T* __restrict__ pos_table,
+                             const int* __restrict__ positions, int max_positions) {
     const int r = blockIdx.x;
     if (r >= rows) return;
     const int id = ids[r];
@@ -25,6 +28,12 @@ __global__ void embed_kernel(float* __restrict__ out, const T* __restrict__ tabl
         return;
     }
     const T* t = table + (size_t)id * width;
+    const int pos = pos_table != nullptr ? positions[r] : -1;
+    if (pos >= 0 && pos < max_positions) {
+        const T* pt = pos_table + (size_t)pos * width;
+        for (int i = threadIdx.x; i < width; i += blockDim.x) o[i] = Elem<T>::load(t + i) * scale + Elem<T>::load(pt + i);
+        return;
+    }
     for (int i = threadIdx.x; i < width; i += blockDim.x) o[i] = Elem<T>::load(t + i) * scale;
 }
 
@@ -41,6 +50,32 @@ __global__ void rope_table_kernel(float2* __restrict__ cos_sin, const int* __res
     double s, c;
     sincos(a, &s, &c);
     cos_sin[i] = make_float2((float)c, (float)s);
+}
+
+// The same from given frequencies (one a pair, 64-bit: a scaling rule was applied on the host), with
+// `magnitude` on both cos and sin.
+__global__ void rope_table_freqs_kernel(float2* __restrict__ cos_sin, const int* __restrict__ positions, int rows,
+                                        int half, const double* __restrict__ freqs, double magnitude) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= rows * half) return;
+    const int r = i / half, j = i % half;
+    const double a = (double)positions[r] * freqs[j];
+    double s, c;
+    sincos(a, &s, &c);
+    cos_sin[i] = make_float2((float)(c * magnitude), (float)(s * magnitude));
+}
+
+// out[r, i] = act(x[r, i]) for a product (a tensor or split-K partial sums): 0 the square of relu, 1 gelu_tanh, 2 silu.
+template <typename TI, typename T>
+__global__ void act_kernel(T* __restrict__ out, const Src<TI> x, long long total, int act) {
+    const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= total) return;
+    const float v = x.at(idx);
+    float a;
+    if (act == 0) { const float r = fmaxf(v, 0.f); a = r * r; }
+    else if (act == 1) a = gelu_tanh(v);
+    else a = v / (1.f + expf(-v));
+    Elem<T>::store(out + idx, a);
 }
 
 // ---------------------------------------------------------------------------------------
@@ -334,18 +369,45 @@ extern "C" int kb_poison(void* x, int dt, long long n, void* stream) {
 }
 
 extern "C" int kb_embed(float* out, const void* table, int table_dt, const int* ids, int rows, int width,
-                        int vocab, float scale, void* stream) {
+                        int vocab, float scale, const void* pos_table, const int* positions, int max_positions, void* stream) {
     KB_REQUIRE(rows >= 0 && width > 0 && vocab > 0, "embed: rows %d, width %d, vocab %d", rows, width, vocab);
+    KB_REQUIRE(pos_table == nullptr || (positions != nullptr && max_positions > 0), "embed: a table of positions without the rows' positions");
     if (rows == 0) return 0;
     cudaStream_t s = (cudaStream_t)stream;
     const int threads = width >= 1024 ? 256 : 128;
     if (table_dt == KB_DT_F32)
-        embed_kernel<float><<<rows, threads, 0, s>>>(out, (const float*)table, ids, rows, width, vocab, scale);
+        embed_kernel<float><<<rows, threads, 0, s>>>(out, (const float*)table, ids, rows, width, vocab, scale, (const float*)pos_table, positions, max_positions);
     else if (table_dt == KB_DT_BF16)
-        embed_kernel<bf16><<<rows, threads, 0, s>>>(out, (const bf16*)table, ids, rows, width, vocab, scale);
+        embed_kernel<bf16><<<rows, threads, 0, s>>>(out, (const bf16*)table, ids, rows, width, vocab, scale, (const bf16*)pos_table, positions, max_positions);
     else
         return fail("embed: table dtype code %d is not known", table_dt);
     return check_launch("embed");
+}
+
+extern "C" int kb_rope_table_freqs(float* cos_sin, const int* positions, int rows, int half, const double* freqs, double magnitude,
+                                   void* stream) {
+    KB_REQUIRE(rows >= 0 && half > 0 && freqs != nullptr, "rope_table_freqs: rows %d, %d pairs", rows, half);
+    if (rows == 0) return 0;
+    const long long n = (long long)rows * half;
+    KB_REQUIRE(n < (1ll << 31), "rope_table_freqs: %lld entries is too many", n);
+    rope_table_freqs_kernel<<<(unsigned)((n + 255) / 256), 256, 0, (cudaStream_t)stream>>>((float2*)cos_sin, positions, rows, half, freqs, magnitude);
+    return check_launch("rope_table_freqs");
+}
+
+extern "C" int kb_act(void* out, int out_dt, const void* x, int in_dt, int splits, long long split_stride, long long total, int act,
+                      void* stream) {
+    KB_REQUIRE(total >= 0 && splits >= 1, "act: %lld values in %d slices", total, splits);
+    KB_REQUIRE(act >= 0 && act <= 2, "act: activation code %d is not known (0 relu squared, 1 gelu_tanh, 2 silu)", act);
+    if (total == 0) return 0;
+    const unsigned blocks = (unsigned)((total + 255) / 256);
+    cudaStream_t s = (cudaStream_t)stream;
+#define KB_ACT(TI, T) act_kernel<TI, T><<<blocks, 256, 0, s>>>((T*)out, Src<TI>{(const TI*)x, splits, (size_t)split_stride}, total, act)
+    if (in_dt == KB_DT_F32 && out_dt == KB_DT_F32) KB_ACT(float, float);
+    else if (in_dt == KB_DT_F32 && out_dt == KB_DT_BF16) KB_ACT(float, bf16);
+    else if (in_dt == KB_DT_BF16 && out_dt == KB_DT_BF16) KB_ACT(bf16, bf16);
+    else return fail("act: dtype codes %d -> %d are not known", in_dt, out_dt);
+#undef KB_ACT
+    return check_launch("act");
 }
 
 extern "C" int kb_rope_table(float* cos_sin, const int* positions, int rows, int rotary, double theta, double divisor,

@@ -1,7 +1,8 @@
 // A mixture of experts: the router, the lists of tokens by expert, the experts' two products as
 // grouped products over those lists, and the weighted sum.
 //
-//  route     z = router . h in 32-bit; s = sigmoid(z) (or softmax over the experts); choice scores
+//  route     z = router . h in 32-bit; s = sigmoid(z) (or softmax over the experts; or z itself, the
+//            chosen experts then weighted by the softmax over the chosen logits alone); choice scores
 //            s + correction; experts in equal groups of neighbours, a group's score the sum of its
 //            `group_top` largest choice scores, only the best `keep_groups` groups stay eligible;
 //            the `top` largest eligible choice scores are chosen (the lower number wins a tie) and
@@ -53,7 +54,9 @@ moe_route_kernel(const TH* __restrict__ h, const float* __restrict__ router, con
     }
     __syncthreads();
     if (threadIdx.x != 0) return;
-    if (softmax) {
+    if (softmax == 2) {
+        // the logits themselves choose; the chosen ones are weighted below
+    } else if (softmax) {
         float mx = -INFINITY;
         for (int x = 0; x < n_experts; ++x) mx = fmaxf(mx, score[x]);
         float total = 0.f;
@@ -118,6 +121,14 @@ moe_route_kernel(const TH* __restrict__ h, const float* __restrict__ router, con
         weights_out[(size_t)r * top + t] = score[best];
         total += score[best];
         state[best] = 2;
+    }
+    if (softmax == 2) {                                      // softmax over the chosen logits alone (the first chosen is the largest)
+        float* w = weights_out + (size_t)r * top;
+        const float mx = w[0];
+        float sum = 0.f;
+        for (int t = 0; t < top; ++t) { w[t] = expf(w[t] - mx); sum += w[t]; }
+        for (int t = 0; t < top; ++t) w[t] /= sum;
+        return;
     }
     if (renormalize && total > 0.f)
         for (int t = 0; t < top; ++t) weights_out[(size_t)r * top + t] /= total;
@@ -372,15 +383,18 @@ moe_grouped_bf16_kernel(const GroupedParams p) {
 }
 
 // ---------------------------------------------------------------------------------------- combine
-template <typename TO>
+// `also` (a tensor or split-K partial sums of the output's shape, or none) is added behind the experts' sum: an
+// expert that every token uses.
+template <typename TO, typename TA>
 __global__ void moe_combine_kernel(TO* __restrict__ out, const float* __restrict__ y, const float* __restrict__ weights,
-                                   long long rows, int width, int top) {
+                                   long long rows, int width, int top, const Src<TA> also) {
     const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= rows * width) return;
     const long long r = i / width;
     const int c = (int)(i - r * width);
     float acc = 0.f;
     for (int t = 0; t < top; ++t) acc = fmaf(weights[r * top + t], y[((size_t)r * top + t) * width + c], acc);
+    if (also.p != nullptr) acc += also.at((size_t)i);
     Elem<TO>::store(out + i, acc);
 }
 
@@ -396,6 +410,7 @@ extern "C" int kb_moe_tile_rows(int dt, long long rows_an_expert) {
 extern "C" int kb_moe_route(int* experts, float* weights, const void* h, int h_dt, const float* router, const float* correction,
                             int rows, int width, int n_experts, int top, int groups, int keep_groups, int group_top,
                             int softmax, int renormalize, void* stream) {
+    KB_REQUIRE(softmax >= 0 && softmax <= 2, "moe_route: scoring code %d is not known (0 sigmoid, 1 softmax, 2 softmax over the chosen)", softmax);
     KB_REQUIRE(rows >= 0 && width > 0 && n_experts > 0 && top > 0 && top <= n_experts, "moe_route: rows %d, width %d, %d experts, top %d", rows, width, n_experts, top);
     KB_REQUIRE(groups >= 1 && n_experts % groups == 0 && keep_groups >= 1 && keep_groups <= groups,
                "moe_route: %d experts in %d groups of which %d are kept", n_experts, groups, keep_groups);
@@ -474,14 +489,20 @@ extern "C" int kb_moe_grouped(void* out, int out_dt, const void* a, const void* 
 }
 
 extern "C" int kb_moe_combine(void* out, int out_dt, const float* y, const float* weights, long long rows, int width, int top,
-                              void* stream) {
+                              const void* also, int also_dt, int also_splits, long long also_stride, void* stream) {
     KB_REQUIRE(rows >= 0 && width > 0 && top > 0, "moe_combine: rows %lld, width %d, top %d", rows, width, top);
+    KB_REQUIRE(also == nullptr || also_splits >= 1, "moe_combine: an addend of %d slices", also_splits);
     if (rows == 0) return 0;
     const long long blocks = (rows * width + 255) / 256;
     KB_REQUIRE(blocks <= 0x7fffffffll, "moe_combine: too many rows for one launch");
     cudaStream_t s = (cudaStream_t)stream;
-    if (out_dt == KB_DT_F32) moe_combine_kernel<float><<<(unsigned)blocks, 256, 0, s>>>((float*)out, y, weights, rows, width, top);
-    else if (out_dt == KB_DT_BF16) moe_combine_kernel<bf16><<<(unsigned)blocks, 256, 0, s>>>((bf16*)out, y, weights, rows, width, top);
+#define KB_COMBINE(TO, TA) \
+    moe_combine_kernel<TO, TA><<<(unsigned)blocks, 256, 0, s>>>((TO*)out, y, weights, rows, width, top, Src<TA>{(const TA*)also, also ? also_splits : 1, (size_t)also_stride})
+    const bool narrow = also != nullptr && also_dt == KB_DT_BF16;
+    KB_REQUIRE(also == nullptr || also_dt == KB_DT_F32 || also_dt == KB_DT_BF16, "moe_combine: addend dtype code %d is not known", also_dt);
+    if (out_dt == KB_DT_F32) { if (narrow) KB_COMBINE(float, bf16); else KB_COMBINE(float, float); }
+    else if (out_dt == KB_DT_BF16) { if (narrow) KB_COMBINE(bf16, bf16); else KB_COMBINE(bf16, float); }
     else return fail("moe_combine: output dtype code %d is not known", out_dt);
+#undef KB_COMBINE
     return check_launch("moe_combine");
 }

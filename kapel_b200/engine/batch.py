@@ -115,6 +115,20 @@ def prompt_split(first_counts, last_counts, pairs_per_tile: int, sms: int, windo
     return (best[1], best[2]) if best else (0, 1)
 
 
+def pooled_slices(rows: int, longest: int, window: Optional[int], pool: int, sms: int, chunk: int):
+    """(slices, keys a slice) of the attention kernel over a window and pooled blocks, which runs one
+    block a row: with few rows, the keys a row can see (the window's tokens and the blocks below it) are
+    cut into slices of a multiple of `chunk` keys so that about two blocks a multiprocessor run."""
+    tokens = min(longest, window) if window else longest
+    keys = tokens + (max(0, longest - window) // pool if (window and pool) else 0)
+    if rows <= 0 or rows >= 2 * sms or keys <= chunk:
+        return 1, 0
+    want = min(-(-keys // chunk), max(1, (2 * sms) // rows))
+    split_keys = -(-(-(-keys // want)) // chunk) * chunk
+    slices = -(-keys // split_keys)
+    return (slices, split_keys) if slices > 1 else (1, 0)
+
+
 _SMS = {}
 
 
@@ -240,6 +254,16 @@ class StepBatch:
             self._slots_memo[window] = max(1, n)
         extra = -(-keep_first // self.chunk) if (window and keep_first) else 0
         return self._slots_memo[window] + extra
+
+    def pooled_slices(self, window: Optional[int], pool: int):
+        """How the attention kernel over a window and pooled blocks cuts this step's keys: (slices, keys a slice)."""
+        key = ("pooled_slices", window, pool)
+        if key not in self.memo:
+            from .. import kernels as K
+
+            longest = int(self.plan.row_count.max()) if self.plan.rows else 0
+            self.memo[key] = pooled_slices(self.plan.rows, longest, window, pool, sm_count(self.ids.device), K.pooled_attention_chunk())
+        return self.memo[key]
 
     def longest_portion(self) -> int:
         """The most rows any request brings in this step (what sizes a launch of a block a run of a request's rows)."""

@@ -19,7 +19,7 @@ from typing import Dict, List, Optional, Tuple
 import numpy as np
 import torch
 
-from .batch import GroupBatch, StepBatch, decode_split, sm_count
+from .batch import GroupBatch, StepBatch, decode_split, pooled_slices, sm_count
 
 ROW_BUCKETS = (1, 2, 4, 8, 16, 24, 32, 48, 64, 96, 128, 192, 256)
 WIDTH_STEP = 64          # block-table widths are rounded up to a multiple of this many pages
@@ -70,6 +70,12 @@ class StaticBatch:
 
     def longest_portion(self) -> int:
         return 1                                             # every request brings one token
+
+    def pooled_slices(self, window: Optional[int], pool: int):
+        """(slices, keys a slice) for the longest request this recording's block tables can hold."""
+        from .. import kernels as K
+
+        return pooled_slices(self.rows, self._longest, window, pool, sm_count(self._device), K.pooled_attention_chunk())
 
     def entry_ranges(self):
         """(start, end) on the device: rows [start[e], end[e]) are request e's (here every row is its own)."""

@@ -59,7 +59,10 @@ class ModelParts:
 
     def forward(self, batch, cache_manager) -> torch.Tensor:
         """float32 logits [wanted rows, vocab] of a step."""
-        x = self.embedding.forward(batch.ids)
+        if getattr(self.embedding, "needs_positions", False):
+            x = self.embedding.forward(batch.ids, batch.positions)
+        else:
+            x = self.embedding.forward(batch.ids)
         schedule = self.spec.schedule
         x0 = None
         if self.merges:

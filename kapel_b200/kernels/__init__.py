@@ -61,7 +61,7 @@ def library():
                 lib = ctypes.CDLL(str(path))
                 lib.kb_last_error.restype = ctypes.c_char_p
                 for name in ("kb_gemm_bf16_scratch_floats", "kb_paged_attention_scratch_floats", "kb_attention_mma_scratch_floats", "kb_sample_scratch_floats",
-                             "kb_mlstm_state_floats", "kb_delta_state_floats", "kb_delta_scratch_floats"):
+                             "kb_mlstm_state_floats", "kb_delta_state_floats", "kb_delta_scratch_floats", "kb_pooled_attention_scratch_floats"):
                     getattr(lib, name).restype = ctypes.c_longlong
                 lib.kb_launch_count.restype = ctypes.c_ulonglong
                 lib.kb_set_pdl(1 if PDL else 0)
@@ -247,16 +247,52 @@ def finish(x, dtype: torch.dtype) -> torch.Tensor:
 
 
 # ------------------------------------------------------------------------------------------
-def embed(table: torch.Tensor, ids: torch.Tensor, scale: float, out: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """out[r] = table[ids[r]] * scale in float32."""
+def embed(table: torch.Tensor, ids: torch.Tensor, scale: float, out: Optional[torch.Tensor] = None,
+          pos_table: Optional[torch.Tensor] = None, positions: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """out[r] = table[ids[r]] * scale in float32; with `pos_table` [max positions, width] (the
+    table's dtype) and the rows' `positions`, plus pos_table[positions[r]] (not scaled)."""
     _need(table, "embed table")
     _need(ids, "embed ids", torch.int32)
     vocab, width = table.shape
     rows = ids.numel()
+    most = 0
+    if pos_table is not None:
+        _need(pos_table, "embed positions' table", table.dtype)
+        if pos_table.dim() != 2 or pos_table.shape[1] != width:
+            raise KernelError(f"embed: a table of positions {tuple(pos_table.shape)} beside rows of {width}")
+        _need(positions, "embed positions", torch.int32, (rows,))
+        most = int(pos_table.shape[0])
     if out is None:
         out = _fresh((rows, width), torch.float32, table.device)
     _need(out, "embed out", torch.float32, (rows, width))
-    _check(library().kb_embed(_ptr(out), _ptr(table), _dt(table, "embed table"), _ptr(ids), rows, width, vocab, _f(scale), _stream()))
+    _check(library().kb_embed(_ptr(out), _ptr(table), _dt(table, "embed table"), _ptr(ids), rows, width, vocab, _f(scale),
+                              _ptr(pos_table), _ptr(positions if pos_table is not None else None), most, _stream()))
+    return out
+
+
+def rope_table_freqs(positions: torch.Tensor, freqs: torch.Tensor, magnitude: float = 1.0) -> torch.Tensor:
+    """[rows, pairs, 2] float32 of (cos, sin) * magnitude of position * freqs[pair]; `freqs` is float64
+    on the device (frequencies that a scaling rule has already changed); angles in float64."""
+    _need(positions, "rope positions", torch.int32)
+    _need(freqs, "rope frequencies", torch.float64)
+    rows, half = positions.numel(), freqs.numel()
+    out = _fresh((rows, half, 2), torch.float32, positions.device)
+    _check(library().kb_rope_table_freqs(_ptr(out), _ptr(positions), rows, int(half), _ptr(freqs), ctypes.c_double(float(magnitude)), _stream()))
+    return out
+
+
+PLAIN_ACT_CODES = {"relu2": 0, "gelu_tanh": 1, "silu": 2}
+
+
+def act(x, activation: str, out_dtype: torch.dtype) -> torch.Tensor:
+    """activation(x) element by element for a product (a tensor or a SplitSum): "relu2" (the square
+    of relu), "gelu_tanh" or "silu"."""
+    src, in_dt, splits, stride = _src(x, "act input")
+    if activation not in PLAIN_ACT_CODES:
+        raise KernelError(f"act: activation {activation!r} is not known ({sorted(PLAIN_ACT_CODES)})")
+    out = _fresh(x.shape, out_dtype, src.device)
+    _check(library().kb_act(_ptr(out), _dt(out, "act output"), _ptr(src), in_dt, splits, ctypes.c_longlong(stride),
+                            ctypes.c_longlong(out.numel()), PLAIN_ACT_CODES[activation], _stream()))
     return out
 
 
@@ -1029,8 +1065,138 @@ def mlstm_scan(stacked, q_off: int, k_off: int, v_off: int, i_off: int, f_off: i
 
 
 # ------------------------------------------------------------------------------------------
+# Attention over a window plus pooled blocks, with the heads' weights mixed.
+def proj_rope_append(stacked, q_off: int, k_off: int, v_off: int, biases, q_norm, k_norm, cos_sin, rotary: int, neighbours: bool,
+                     v_other: Optional[torch.Tensor], v_weight: Optional[torch.Tensor], keep_values: bool, lines, k_table, v_table,
+                     hq: int, hkv: int, d: int, dv: int, write_kv: bool, out_dtype: torch.dtype):
+    """q [rows, hq, d] from the columns q_off.. of `stacked` (a tensor or a SplitSum): plus the bias
+    `biases[0]`, normed over the whole projection when `q_norm` = (weight [hq d], eps, offset) is given,
+    the first `rotary` components of every head turned by `cos_sin` [rows, rotary/2, 2] (pairs
+    (i, i + rotary/2), or (2i, 2i+1) with `neighbours`). Keys likewise (`biases[1]`, `k_norm`) and written
+    at each row's line of the table [pages, hkv, page_size, d]. Values: plus `biases[2]`; with `v_other`
+    [rows, hkv dv] float32 and `v_weight` (one value l on the device) v <- (1 - l) v + l v_other; written
+    to the table [.., dv]. Returns (q, the values before that mix as float32 [rows, hkv dv] if
+    `keep_values`, else None). Biases and norm weights share a dtype."""
+    src, dt, splits, stride, rows, width = _stacked(stacked, "proj_rope_append input")
+    bq, bk, bv = biases if biases is not None else (None, None, None)
+    wq, eq, oq = q_norm if q_norm is not None else (None, 0.0, 0.0)
+    wk, ek, ok = k_norm if k_norm is not None else (None, 0.0, 0.0)
+    small = [t for t in (bq, bk, bv, wq, wk, v_weight) if t is not None]
+    if len({t.dtype for t in small}) > 1:
+        raise KernelError("proj_rope_append: biases, norm weights and the values' weight differ in dtype")
+    for t, n, what in ((bq, hq * d, "q bias"), (bk, hkv * d, "k bias"), (bv, hkv * dv, "v bias"), (wq, hq * d, "q norm"), (wk, hkv * d, "k norm")):
+        if t is not None:
+            _need(t, f"proj_rope_append {what}", shape=(n,))
+    w_dt = _dt(small[0], "proj_rope_append weights") if small else F32
+    if rotary:
+        _need(cos_sin, "proj_rope_append rotation table", torch.float32, (rows, rotary // 2, 2))
+    if (v_other is None) != (v_weight is None):
+        raise KernelError("proj_rope_append: other values and their weight come together")
+    if v_other is not None:
+        _need(v_other, "proj_rope_append other values", torch.float32, (rows, hkv * dv))
+        if v_weight.numel() != 1:
+            raise KernelError(f"proj_rope_append: the values' weight has {v_weight.numel()} values")
+    q = _fresh((rows, hq, d), out_dtype, src.device)
+    kept = _fresh((rows, hkv * dv), torch.float32, src.device) if keep_values else None
+    table_lines, page_size = 0, 0
+    if write_kv:
+        _need(lines, "proj_rope_append lines", torch.int32, (rows,))
+        _need(k_table, "proj_rope_append k table", out_dtype)
+        _need(v_table, "proj_rope_append v table", out_dtype)
+        if k_table.dim() != 4 or k_table.shape[1] != hkv or k_table.shape[3] != d or v_table.dim() != 4 or \
+                tuple(v_table.shape) != (*k_table.shape[:3], dv):
+            raise KernelError(f"proj_rope_append: tables {tuple(k_table.shape)} / {tuple(v_table.shape)} are not [pages, {hkv}, page_size, {d} / {dv}]")
+        table_lines = k_table.shape[0] * k_table.shape[2]
+        page_size = k_table.shape[2]
+    _check(library().kb_proj_rope_append(
+        _ptr(src), dt, splits, ctypes.c_longlong(stride), width, int(q_off), int(k_off), int(v_off), _ptr(bq), _ptr(bk), _ptr(bv),
+        _ptr(wq), _f(eq), _f(oq), _ptr(wk), _f(ek), _f(ok), w_dt, _ptr(cos_sin if rotary else None), int(rotary), int(bool(neighbours)),
+        _ptr(v_other), _ptr(v_weight), _ptr(kept), _ptr(lines if write_kv else None), _ptr(q), _ptr(k_table if write_kv else None),
+        _ptr(v_table if write_kv else None), _CODES[out_dtype], rows, hq, hkv, d, dv, int(bool(write_kv)),
+        ctypes.c_longlong(table_lines), int(page_size), _stream()))
+    return q, kept
+
+
+def pool_blocks(k_table, v_table, block_table, row_entry, positions, lines, slots, pooled: torch.Tensor, pool: int) -> None:
+    """For every row whose position ends a block of `pool` positions: the means of the block's keys and
+    of its values, read back from the cache, into pooled[slot of the row's request, block] (`pooled` is
+    float32 [slots, blocks, kv_heads, d + dv])."""
+    _need(k_table, "pool_blocks k table")
+    _need(v_table, "pool_blocks v table", k_table.dtype)
+    _need(pooled, "pool_blocks means", torch.float32)
+    n_pages, hkv, page_size, d = k_table.shape
+    dv = v_table.shape[3]
+    if pooled.dim() != 4 or pooled.shape[2] != hkv or pooled.shape[3] != d + dv:
+        raise KernelError(f"pool_blocks: means {tuple(pooled.shape)} are not [slots, blocks, {hkv}, {d + dv}]")
+    rows = positions.numel()
+    for t, what in ((row_entry, "row_entry"), (positions, "positions"), (lines, "lines")):
+        _need(t, f"pool_blocks {what}", torch.int32, (rows,))
+    _need(slots, "pool_blocks slots", torch.int32)
+    _need(block_table, "pool_blocks block table", torch.int32)
+    _check(library().kb_pool_blocks(
+        _ptr(k_table), _ptr(v_table), _dt(k_table, "pool_blocks k table"), _ptr(block_table), int(block_table.shape[1]), int(n_pages),
+        _ptr(row_entry), _ptr(positions), _ptr(lines), _ptr(slots), _ptr(pooled), ctypes.c_longlong(pooled.stride(0)), int(pooled.shape[0]),
+        int(pooled.shape[1]), int(pool), rows, int(hkv), int(d), int(dv), int(page_size), _stream()))
+
+
+_POOLED_CHUNK = None
+
+
+def pooled_attention_chunk() -> int:
+    """Keys a step of the kernel below: slices of the keys are multiples of it."""
+    global _POOLED_CHUNK
+    if _POOLED_CHUNK is None:
+        _POOLED_CHUNK = int(library().kb_pooled_attention_chunk())
+    return _POOLED_CHUNK
+
+
+def pooled_attention(q, k_table, v_table, pooled: Optional[torch.Tensor], block_table, row_entry, row_count, slots, talk, temp,
+                     page_size: int, window: Optional[int], pool: int, scale: float, splits: int = 1, split_keys: int = 0) -> torch.Tensor:
+    """Attention of each query row [rows, hq, d] over the last `window` tokens of its sequence (all with
+    `window` None) and the pooled blocks of `pool` positions that lie wholly below the window (their mean
+    keys and values in `pooled` [slots, blocks, hkv, d + dv], float32), in one softmax; score = q.k * scale
+    * temp[h]; then the heads' weights are mixed by `talk` [hq, hq] (float32; None: no mix) ahead of the
+    values. With `splits` > 1 the keys are cut into that many slices of `split_keys` across blocks."""
+    rows, hq, d = q.shape
+    _need(q, "pooled attention q")
+    _need(k_table, "pooled attention k table", q.dtype)
+    _need(v_table, "pooled attention v table", q.dtype)
+    if k_table.dim() != 4 or k_table.shape[2] != page_size or k_table.shape[3] != d or v_table.dim() != 4 or v_table.shape[:3] != k_table.shape[:3]:
+        raise KernelError(f"pooled attention: tables {tuple(k_table.shape)} / {tuple(v_table.shape)} are not [pages, kv_heads, {page_size}, {d}]")
+    n_pages, hkv, dv = k_table.shape[0], k_table.shape[1], v_table.shape[3]
+    n_slots = max_blocks = 0
+    stride = 0
+    if pool:
+        _need(pooled, "pooled attention means", torch.float32)
+        if pooled.dim() != 4 or pooled.shape[2] != hkv or pooled.shape[3] != d + dv:
+            raise KernelError(f"pooled attention: means {tuple(pooled.shape)} are not [slots, blocks, {hkv}, {d + dv}]")
+        n_slots, max_blocks, stride = int(pooled.shape[0]), int(pooled.shape[1]), int(pooled.stride(0))
+    if talk is not None:
+        _need(talk, "pooled attention head mix", torch.float32, (hq, hq))
+    if temp is not None:
+        _need(temp, "pooled attention head temperatures", torch.float32, (hq,))
+    _need(block_table, "pooled attention block table", torch.int32)
+    _need(row_entry, "pooled attention row_entry", torch.int32, (rows,))
+    _need(row_count, "pooled attention row_count", torch.int32, (rows,))
+    _need(slots, "pooled attention slots", torch.int32)
+    out = _fresh((rows, hq, dv), q.dtype, q.device)
+    lib = library()
+    need = lib.kb_pooled_attention_scratch_floats(rows, hq, int(dv), int(splits))
+    scratch = _fresh((need,), torch.float32, q.device) if need else None
+    _check(lib.kb_pooled_attention(
+        _ptr(out), _ptr(q), _ptr(k_table), _ptr(v_table), _dt(q, "pooled attention q"), _ptr(pooled if pool else None),
+        ctypes.c_longlong(stride), n_slots, max_blocks, _ptr(block_table), _ptr(row_entry), _ptr(row_count), _ptr(slots), _ptr(talk),
+        _ptr(temp), rows, hq, int(hkv), d, int(dv), int(page_size), int(block_table.shape[1]), int(n_pages), int(window or 0), int(pool or 0),
+        _f(scale), int(splits), int(split_keys), _ptr(scratch), _stream()))
+    return out
+
+
+# ------------------------------------------------------------------------------------------
 # Mixture of experts.
 MOE_ACT_CODES = {"none": 0, "relu2": 1, "gelu_tanh": 2, "silu": 3}
+# How the router's logits z become scores: sigmoid(z); the softmax over all experts; or "softmax_chosen":
+# z itself chooses and the chosen experts are weighted by the softmax over their logits alone.
+ROUTE_SCORING = {"sigmoid": 0, "softmax": 1, "softmax_chosen": 2}
 
 
 def moe_route(h: torch.Tensor, router: torch.Tensor, correction: Optional[torch.Tensor], top: int, groups: int, keep_groups: int,
@@ -1045,13 +1211,13 @@ def moe_route(h: torch.Tensor, router: torch.Tensor, correction: Optional[torch.
         raise KernelError(f"moe_route: router {tuple(router.shape)} against rows of {width}")
     if correction is not None:
         _need(correction, "moe_route correction", torch.float32, (n_experts,))
-    if scoring not in ("sigmoid", "softmax"):
-        raise KernelError(f"moe_route: scoring {scoring!r} is not known")
+    if scoring not in ROUTE_SCORING:
+        raise KernelError(f"moe_route: scoring {scoring!r} is not known ({sorted(ROUTE_SCORING)})")
     experts = _fresh((rows, top), torch.int32, h.device)
     weights = _fresh((rows, top), torch.float32, h.device)
     _check(library().kb_moe_route(_ptr(experts), _ptr(weights), _ptr(h), _dt(h, "moe_route input"), _ptr(router), _ptr(correction),
                                   rows, width, n_experts, int(top), int(groups), int(keep_groups), int(group_top),
-                                  int(scoring == "softmax"), int(bool(renormalize)), _stream()))
+                                  ROUTE_SCORING[scoring], int(bool(renormalize)), _stream()))
     return experts, weights
 
 
@@ -1104,16 +1270,23 @@ def moe_grouped(a: torch.Tensor, w: torch.Tensor, lists: ExpertLists, act: str, 
     return out
 
 
-def moe_combine(y: torch.Tensor, weights: torch.Tensor, out_dtype: torch.dtype) -> torch.Tensor:
-    """out[token] = sum over k, in order, of weights[token, k] * y[token * top + k]."""
+def moe_combine(y: torch.Tensor, weights: torch.Tensor, out_dtype: torch.dtype, also=None) -> torch.Tensor:
+    """out[token] = sum over k, in order, of weights[token, k] * y[token * top + k], plus `also`[token]
+    where given (a tensor or a SplitSum [tokens, width]: the output of an expert that every token uses)."""
     _need(y, "moe_combine input", torch.float32)
     _need(weights, "moe_combine weights", torch.float32)
     rows, top = weights.shape
     width = y.shape[1]
     if y.shape[0] != rows * top:
         raise KernelError(f"moe_combine: {y.shape[0]} rows for {rows} tokens of {top} experts")
+    a_src, a_dt, a_splits, a_stride = (None, F32, 1, 0)
+    if also is not None:
+        a_src, a_dt, a_splits, a_stride = _src(also, "moe_combine addend")
+        if tuple(also.shape) != (rows, width):
+            raise KernelError(f"moe_combine: an addend {tuple(also.shape)} beside a sum of {(rows, width)}")
     out = _fresh((rows, width), out_dtype, y.device)
-    _check(library().kb_moe_combine(_ptr(out), _CODES[out_dtype], _ptr(y), _ptr(weights), ctypes.c_longlong(rows), int(width), int(top), _stream()))
+    _check(library().kb_moe_combine(_ptr(out), _CODES[out_dtype], _ptr(y), _ptr(weights), ctypes.c_longlong(rows), int(width), int(top),
+                                    _ptr(a_src), a_dt, int(a_splits), ctypes.c_longlong(a_stride), _stream()))
     return out
 
 

@@ -5,7 +5,7 @@ from .base import (BuildContext, LayerCache, Part, linear, matrix_for, matrix_na
 from .block import PostNormBlock, PreNormBlock, SandwichBlock
 from .delta import Delta
 from .embedding import Embedding, VocabHead
-from .feed_forward import GatedMLP
+from .feed_forward import MLP, GatedMLP
 from .input_mix import InputMix
 from .latent_attention import LatentAttention
 from .mlstm import MLSTM
@@ -30,6 +30,7 @@ register_part("mixer", "latent_attention", LatentAttention)
 register_part("mixer", "delta", Delta)
 register_part("merge", "input_mix", InputMix)
 register_part("feed_forward", "gated_mlp", GatedMLP)
+register_part("feed_forward", "mlp", MLP)
 register_part("feed_forward", "moe", MoE)
 register_part("norm", "rms", RMSNorm)
 register_part("norm", "layer", LayerNorm)
@@ -45,6 +46,8 @@ register_part("head", "vocab_head", VocabHead)
 def expected_tensors(spec) -> dict:
     """{tensor name: shape} of everything a model built from `spec` reads."""
     out = {spec.embed.weight: (spec.vocab_size, spec.hidden_size)}
+    if getattr(spec.embed, "positions", None):
+        out[spec.embed.positions] = (spec.embed.max_positions, spec.hidden_size)
     out[spec.head.weight] = (spec.vocab_size, spec.hidden_size)
     n = spec.final_norm
     out.update(part_class("norm", n.kind).expected_tensors(n))

@@ -16,13 +16,19 @@ A spec with an RMS norm over every head's query and key (`q_head_norm`, `k_head_
 of the head's size for all heads) runs the third path: the stacked product in 32-bit, one kernel
 that norms each head, rotates it and appends keys and values (of their own size) to the cache,
 then the tensor-core kernels where keys and values have one size and the row-wise kernel elsewhere.
+
+A spec with biases, pooled blocks below the window, a number a head on the scores, mixed heads'
+weights or values mixed with another layer's runs the fourth path (`forward_pooled`): the stacked
+product in 32-bit; one kernel for biases, the norms over the whole projections, the rotation (either
+pairing), the value mix and the append; one that leaves the means of every block the step completes
+in the request's slot of the layer's state table; then the attention kernel over window and blocks.
 """
 from __future__ import annotations
 
 import torch
 
 from .. import kernels as K
-from ..cache import CacheNeeds, PagedKV
+from ..cache import CacheNeeds, PagedKV, StateSpec
 from .base import Part, linear, matrix_named, pad_columns, product_width, require_product_widths, stack_rows
 from .registry import build_part
 
@@ -42,6 +48,14 @@ class Attention(Part):
         for n in (spec.q_norm, spec.k_norm, spec.q_head_norm, spec.k_head_norm):
             if n is not None:
                 out[n.weight] = (n.width,)
+        if spec.bias:
+            out[w["q_bias"]], out[w["k_bias"]], out[w["v_bias"]] = (qd,), (kvd,), (spec.num_kv_heads * dv,)
+        if spec.head_temp:
+            out[w["temp"]] = (spec.num_heads,)
+        if spec.talk:
+            out[w["talk"]] = (spec.num_heads, spec.num_heads)
+        if spec.value_mix == "mix":
+            out[w["vmix"]] = ()
         return out
 
     def __init__(self, spec, ctx):
@@ -50,33 +64,52 @@ class Attention(Part):
             raise ValueError(f"attention: {spec.num_heads} heads over {spec.num_kv_heads} kv heads")
         self.v_dim = spec.v_head_dim or spec.head_dim
         self.by_head = bool(spec.q_head_norm or spec.k_head_norm)
-        self.general = bool(spec.gated or spec.q_norm or spec.k_norm or spec.keep_first or self.v_dim != spec.head_dim) and not self.by_head
+        self.pooled = bool(spec.bias or spec.pool or spec.head_temp or spec.talk or spec.value_mix)
+        if self.pooled:
+            if self.by_head or spec.gated or spec.keep_first or spec.softcap:
+                raise ValueError("attention: biases, pooled blocks, head temperatures, mixed heads or mixed values together with norms "
+                                 "over each head, a gate, kept first keys or a soft cap are not built")
+            if spec.pool and (not spec.window or spec.pool_blocks <= 0):
+                raise ValueError(f"attention: blocks of {spec.pool} need a window (got {spec.window}) and a count of blocks (got {spec.pool_blocks})")
+            if spec.value_mix not in (None, "source", "mix"):
+                raise ValueError(f"attention: value_mix {spec.value_mix!r} is not known (\"source\", \"mix\")")
+        self.general = bool(spec.gated or spec.q_norm or spec.k_norm or spec.keep_first or self.v_dim != spec.head_dim) and not self.by_head \
+            and not self.pooled
         if self.by_head and (spec.q_norm or spec.k_norm or spec.keep_first or spec.window):
             raise ValueError("attention: norms over each head together with norms over the whole projection, a window or kept first keys are not built")
         for n in (spec.q_head_norm, spec.k_head_norm):
             if n is not None and (n.kind != "rms" or n.width != spec.head_dim):
                 raise ValueError(f"attention: a norm over each head must be an RMS norm of width {spec.head_dim}")
-        if not self.general and not self.by_head and spec.head_dim % 16:
+        if not self.general and not self.by_head and not self.pooled and spec.head_dim % 16:
             raise ValueError(f"attention: head_dim {spec.head_dim} must be a multiple of 16 for the kernels")
         if spec.keep_first < 0 or (spec.keep_first and not spec.window):
             raise ValueError(f"attention: {spec.keep_first} first keys kept with window {spec.window}")
         for n, width in ((spec.q_norm, spec.num_heads * spec.head_dim), (spec.k_norm, spec.num_kv_heads * spec.head_dim)):
             if n is not None and (n.kind != "rms" or n.width != width):
                 raise ValueError(f"attention: a norm over the whole projection must be an RMS norm of width {width}")
-        if not self.general and not self.by_head:
+        if not self.general and not self.by_head and not self.pooled:
             require_product_widths(ctx, "attention", hidden_size=spec.hidden,
                                    **{"num_attention_heads x value size": spec.num_heads * self.v_dim})
         self.position = build_part("position", spec.position, ctx)
         if self.general and self.position.rotary_dim:
             raise ValueError("attention: a rotation together with projection norms, a gate, kept first keys or another value size is not built")
+        if not self.pooled and getattr(self.position, "neighbours", False):
+            raise ValueError("attention: the rotation of neighbouring components is built for the path with biases, pooled blocks or mixed heads only")
 
     def load(self, tensors):
         w = self.spec.weights
         names = [w["q"], w["k"], w["v"]] + ([w["g"]] if self.spec.gated else [])
         self.w_qkv = stack_rows(self.ctx, tensors, names, "attention")
         self.w_o = matrix_named(self.ctx, tensors, w["o"])
-        if (self.general and self.spec.gated) or self.by_head:
+        if (self.general and self.spec.gated) or self.by_head or self.pooled:
             self.w_o = pad_columns(self.ctx, self.w_o)
+        if self.pooled:
+            dev = self.ctx.device
+            small = lambda name: (tensors[name].to(dev).float() if self.ctx.is_f32 else tensors[name].to(dev)).contiguous()
+            self.biases = tuple(small(w[r]) for r in ("q_bias", "k_bias", "v_bias")) if self.spec.bias else None
+            self.temp = tensors[w["temp"]].to(dev).float().contiguous() if self.spec.head_temp else None
+            self.talk = tensors[w["talk"]].to(dev).float().contiguous() if self.spec.talk else None
+            self.v_weight = small(w["vmix"]).reshape(1) if self.spec.value_mix == "mix" else None
         self.proj_norms = []
         for n in (self.spec.q_head_norm, self.spec.k_head_norm) if self.by_head else (self.spec.q_norm, self.spec.k_norm):
             if n is None:
@@ -88,8 +121,47 @@ class Attention(Part):
 
     def cache_needs(self) -> CacheNeeds:
         s = self.spec
+        if self.pooled and s.pool:
+            # The pages keep the window's tokens, and a block's tokens until its last one has come (the
+            # means are taken from the pages then); the means of a request's blocks are its state.
+            kept = max(s.window, s.pool)
+            return CacheNeeds(paged=PagedKV(s.num_kv_heads, s.head_dim, kept, 0, self.v_dim if self.v_dim != s.head_dim else None),
+                              state=StateSpec((s.pool_blocks, s.num_kv_heads, s.head_dim + self.v_dim)))
         return CacheNeeds(paged=PagedKV(s.num_kv_heads, s.head_dim, s.window, s.keep_first if s.window else 0,
                                         self.v_dim if self.v_dim != s.head_dim else None))
+
+    def forward_pooled(self, h, batch, cache):
+        s, dv = self.spec, self.v_dim
+        nq, nk = s.num_heads * s.head_dim, s.num_kv_heads * s.head_dim
+        stacked = linear(self.ctx, h, self.w_qkv, out_dtype=torch.float32, keep_split=True)
+        k_table, v_table = cache.tables()
+        group = batch.groups[cache.group]
+        rotary = self.position.rotary_dim
+        v_other = None
+        if s.value_mix == "mix":
+            v_other = batch.memo.get(("value_mix", s.value_mix_key))
+            if v_other is None:
+                raise ValueError(f"attention: values are mixed with those of {s.value_mix_key!r}, which no earlier layer of the step has kept")
+        q, kept = K.proj_rope_append(
+            stacked, 0, nq, nq + nk, self.biases, self.proj_norms[0], self.proj_norms[1],
+            self.position.tables(batch) if rotary else None, rotary, getattr(self.position, "neighbours", False),
+            v_other, self.v_weight if v_other is not None else None, s.value_mix == "source", group.lines, k_table, v_table,
+            s.num_heads, s.num_kv_heads, s.head_dim, dv, cache.owns, self.ctx.dtype)
+        if kept is not None:
+            batch.memo[("value_mix", s.value_mix_key)] = kept
+        pooled = None
+        if s.pool:
+            pooled = cache.state()
+            if cache.owns:
+                K.pool_blocks(k_table, v_table, group.block_table, batch.row_entry, batch.positions, group.lines, batch.slots, pooled, s.pool)
+        splits, split_keys = batch.pooled_slices(s.window, s.pool) if hasattr(batch, "pooled_slices") else (1, 0)
+        y = K.pooled_attention(q, k_table, v_table, pooled, group.block_table, batch.row_entry, batch.row_count, batch.slots,
+                               self.talk, self.temp, self.ctx.page_size, s.window, s.pool, s.scale, splits, split_keys)
+        width = product_width(self.ctx, s.num_heads * dv)
+        y = y.view(y.shape[0], s.num_heads * dv)
+        if width != y.shape[1]:
+            y = K.pad_cols(y, width)
+        return linear(self.ctx, y, self.w_o, keep_split=True)
 
     def forward_general(self, h, batch, cache):
         s, dv = self.spec, self.v_dim
@@ -151,6 +223,8 @@ class Attention(Part):
 
     def forward(self, h, batch, cache):
         s = self.spec
+        if self.pooled:
+            return self.forward_pooled(h, batch, cache)
         if self.by_head:
             return self.forward_by_head(h, batch, cache)
         if self.general:

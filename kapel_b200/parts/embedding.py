@@ -18,10 +18,20 @@ class Embedding(Part):
 
     @staticmethod
     def expected_tensors(spec):
-        return {}          # the table's shape is the model's [vocab, hidden]; ModelParts adds it
+        return {}          # the table's shape is the model's [vocab, hidden]; ModelParts adds it (and the positions' table)
+
+    @property
+    def needs_positions(self) -> bool:
+        """Whether `forward` wants the rows' positions beside their token ids (a table of learned positions)."""
+        return bool(getattr(self.spec, "positions", None))
 
     def load(self, tensors):
         self.table = matrix_named(self.ctx, tensors, self.spec.weight)
+        self.pos_table = None
+        if self.needs_positions:
+            self.pos_table = matrix_named(self.ctx, tensors, self.spec.positions)
+            if self.pos_table.dtype != self.table.dtype:
+                self.pos_table = self.pos_table.to(self.table.dtype)
         scale = float(self.spec.scale)
         if self.spec.round_scale and self.ctx.dtype == torch.bfloat16:
             scale = float(torch.tensor(scale, dtype=torch.float32).to(torch.bfloat16).float())
@@ -29,7 +39,11 @@ class Embedding(Part):
             scale = float(torch.tensor(scale, dtype=torch.float32))
         self.scale = scale
 
-    def forward(self, ids):
+    def forward(self, ids, positions=None):
+        if self.pos_table is not None:
+            if positions is None:
+                raise ValueError("embedding: a table of learned positions needs the rows' positions")
+            return K.embed(self.table, ids, self.scale, pos_table=self.pos_table, positions=positions)
         return K.embed(self.table, ids, self.scale)
 
 

@@ -1,5 +1,6 @@
 """The gated feed-forward: down(act(gate(h)) * up(h)), gate and up as one stacked product
-(crates/kapel-models/src/model.rs:1429-1456; the gated unit kernels/src/lib.rs glu_any :2489)."""
+(crates/kapel-models/src/model.rs:1429-1456; the gated unit kernels/src/lib.rs glu_any :2489); and
+the plain one, down(act(up(h))), whose activation is a kernel of its own between the two products."""
 from __future__ import annotations
 
 import torch
@@ -38,4 +39,31 @@ class GatedMLP(Part):
         if inner is None:
             gu = linear(self.ctx, h, self.w_gate_up, keep_split=True)
             inner = K.glu(gu, self.spec.activation, out_dtype=self.ctx.dtype)
+        return linear(self.ctx, inner, self.w_down, keep_split=True)
+
+
+class MLP(Part):
+    """down(act(up(h))) without a gate; the activation reads the first product's sums in 32-bit
+    (split over K or not) and leaves the second product's input."""
+
+    graph_safe = True
+
+    @staticmethod
+    def expected_tensors(spec):
+        w = spec.weights
+        return {w["up"]: (spec.intermediate, spec.hidden), w["down"]: (spec.hidden, spec.intermediate)}
+
+    def __init__(self, spec, ctx):
+        super().__init__(spec, ctx)
+        if spec.activation not in K.PLAIN_ACT_CODES:
+            raise ValueError(f"mlp: activation {spec.activation!r} is not built")
+
+    def load(self, tensors):
+        w = self.spec.weights
+        self.w_up = matrix_named(self.ctx, tensors, w["up"])
+        self.w_down = matrix_named(self.ctx, tensors, w["down"])
+
+    def forward(self, h):
+        up = linear(self.ctx, h, self.w_up, out_dtype=torch.float32, keep_split=True)
+        inner = K.act(up, self.spec.activation, self.ctx.dtype)
         return linear(self.ctx, inner, self.w_down, keep_split=True)
