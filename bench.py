@@ -1,7 +1,7 @@
 """Throughput of the engine at Gemma 2 sizes with random weights, on one GPU.
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--size 2b|9b|27b] [--layers L] [--impl reference]
-    python bench.py --design fusitar|kofutar [--design-sizes s,m]      (another line: see `design_line`)
+    python bench.py --design fusitar|kofutar|teluzen [--design-sizes s,m]      (another line: see `design_line`)
 
 A "step" is one decode step. The default run has the layer sizes of the 2B configuration
 (26 layers, hidden 2304, 8 heads over 4 kv heads of 256, intermediate 9216, vocabulary 256000,
@@ -407,6 +407,26 @@ def kofutar_config(z):
 KOFUTAR_KV_RANK = 512
 
 
+# --design teluzen: the Teluzen design (attention over a window plus pooled blocks below it, biases, norms over the
+# whole projections, scaled rotation of neighbours, a number a head, mixed heads' weights, values mixed with the first
+# layer's; a plain feed-forward in the first layer and gated experts with a shared expert in the others; learned
+# positions) beside Fusitar, the engine's other design with windowed attention and experts, and Gemma 2, at equal
+# sizes: the same width, heads, head size, window, vocabulary, as many layers, and as much feed-forward a token
+# (top - 1 chosen experts and the shared one of the expert's size; the first layer's plain one of Gemma's size).
+TELUZEN_POOL = 16
+TELUZEN_POSITIONS = 8192
+
+
+def teluzen_config(z):
+    rot = {"base": 10000.0, "dims": z["dim"] // 2, "scaling": {"factor": 8.0, "original": 1024, "fast": 32.0, "slow": 1.0}}
+    mixer = {"heads": z["heads"], "kv_heads": z["kv_heads"], "dim": z["dim"], "vdim": z["dim"], "scale": z["dim"] ** -0.5,
+             "mask": {"size": z["window"], "pool": TELUZEN_POOL}, "rot": rot, "v_mix": True}
+    moe = {"kind": "moe", "expert": {"ff": z["ff"]}, "router": {"experts": z["experts"], "top": z["top"] - 1}, "shared": {"ff": z["ff"]}}
+    dense = {"kind": "dense", "ff": z["top"] * z["ff"]}
+    return {"architecture": "Teluzen", "vocab": z["vocab"], "width": z["width"], "max_positions": TELUZEN_POSITIONS, "norm": {"eps": 1e-6},
+            "layers": [{"type": "attention", "mixer": mixer, "mlp": dense if i == 0 else moe} for i in range(z["layers"])]}
+
+
 def gemma_config(z):
     return {"architectures": ["Gemma2ForCausalLM"], "model_type": "gemma2", "num_hidden_layers": z["layers"], "hidden_size": z["width"],
             "num_attention_heads": z["heads"], "num_key_value_heads": z["kv_heads"], "head_dim": z["dim"],
@@ -420,6 +440,18 @@ def design_kernel_rooflines(which, z, kind, rows, context, batch, pk):
     tokens of one request from position 0) or "decode" (batch requests of `context` positions)."""
     w, hq, hkv, d, win = z["width"], z["heads"], z["kv_heads"], z["dim"], z["window"]
     layers = z["layers"]
+    if which == "teluzen":
+        # a query that has seen c positions reads min(c, window) tokens and the blocks wholly below its window; scores,
+        # the mix of the heads' weights (hq x hq a key) and the values; the blocks' means are 32-bit in the state
+        seen = lambda c: min(c, win) + (max(0, c - win) // TELUZEN_POOL)
+        moe_layers = layers - 1
+        if kind == "prefill":
+            pairs = sum(seen(c) for c in range(1, rows + 1))
+            return {"attention": ("flops", layers * 2.0 * pairs * hq * (2 * d + hq)),
+                    "feed_forward": ("flops", 2.0 * rows * 2 * z["top"] * z["ff"] * w + moe_layers * 2.0 * rows * 3 * z["top"] * z["ff"] * w)}
+        experts_read = min(z["experts"], batch * (z["top"] - 1)) + 1
+        return {"attention": ("bytes", layers * batch * (min(context, win) * hkv * 2 * d * 2.0 + (max(0, context - win) // TELUZEN_POOL) * hkv * 2 * d * 4.0)),
+                "feed_forward": ("bytes", 2.0 * z["top"] * z["ff"] * w * 2 + moe_layers * experts_read * 3.0 * z["ff"] * w * 2)}
     if which == "kofutar":
         att_layers, lat_layers, rec_layers = (layers + 3) // 4, (layers + 1) // 4, layers // 2
         r, kv, ff = 64, KOFUTAR_KV_RANK, z["top"] * z["ff"]
@@ -460,6 +492,13 @@ KOFUTAR_KERNEL_CLASSES = {
     "feed_forward": ("gemm_glu_fused", "glu"),
     "delta_scan": ("delta_scan",),
 }
+# Teluzen's attention is the kernel over window and blocks (the means of the blocks a step completes included); its
+# feed-forwards are the grouped products with the gated unit between them, the shared expert's fused product, the plain
+# layer's activation, and the plain products whose inner width is an expert's or the plain layer's size.
+TELUZEN_KERNEL_CLASSES = {
+    "attention": ("pooled_attention", "pooled_attention_mma", "pool_blocks"),
+    "feed_forward": ("moe_grouped", "gemm_glu_fused", "glu", "act"),
+}
 
 
 def design_point(which, z, steps, warmup, clocks, pk):
@@ -471,7 +510,7 @@ def design_point(which, z, steps, warmup, clocks, pk):
     from kapel_b200 import kernels as K
     from kapel_b200.engine import Engine, StepEntry
 
-    cfg = {"fusitar": fusitar_config, "kofutar": kofutar_config, "gemma2": gemma_config}[which](z)
+    cfg = {"fusitar": fusitar_config, "kofutar": kofutar_config, "gemma2": gemma_config, "teluzen": teluzen_config}[which](z)
     room = (DESIGN_BATCH + 1) * (DESIGN_HISTORY + 4 * (steps + warmup) + 128) + PREFILL_TOKENS
     engine = Engine.random(cfg, seed=0, dtype="bfloat16", max_tokens=room, max_sequences=DESIGN_BATCH + 2)
     rng = np.random.default_rng(0)
@@ -516,7 +555,7 @@ def design_point(which, z, steps, warmup, clocks, pk):
         must = design_kernel_rooflines(which, z, kind, PREFILL_TOKENS, DESIGN_HISTORY, DESIGN_BATCH, pk)
         classes = {}
         for name, shape, calls, ms in rows:
-            for cls, members in (KOFUTAR_KERNEL_CLASSES if which == "kofutar" else KERNEL_CLASSES).items():
+            for cls, members in {"kofutar": KOFUTAR_KERNEL_CLASSES, "teluzen": TELUZEN_KERNEL_CLASSES}.get(which, KERNEL_CLASSES).items():
                 if name in members:
                     classes[cls] = classes.get(cls, 0.0) + ms
         if which in ("gemma2", "kofutar"):   # the dense way down is a plain product: count the products whose inner width is the intermediate size
@@ -524,6 +563,9 @@ def design_point(which, z, steps, warmup, clocks, pk):
             classes["feed_forward"] = classes.get("feed_forward", 0.0) + sum(
                 ms * (z["layers"] / calls if (which == "kofutar" and calls == z["layers"] + 1) else 1.0)
                 for name, shape, calls, ms in rows if name == "gemm" and len(shape) == 2 and shape[0] == z["width"] and shape[1] == z["top"] * z["ff"])
+        if which == "teluzen":             # the ways down of the plain layer and of the shared expert
+            classes["feed_forward"] = classes.get("feed_forward", 0.0) + sum(
+                ms for name, shape, calls, ms in rows if name == "gemm" and len(shape) == 2 and shape[0] == z["width"] and shape[1] in (z["ff"], z["top"] * z["ff"]))
         rec = {"kernels": [{"name": n, "shape": list(sh), "calls": c, "ms": round(ms, 4)} for n, sh, c, ms in rows][:14], "classes": {}}
         for cls, ms in classes.items():
             unit, amount = must[cls]
@@ -552,6 +594,8 @@ def design_line(args) -> int:
     for name in args.design_sizes.split(","):
         z = DESIGN_SIZES[name]
         beside = ("gemma2",) if args.design == "fusitar" else ("fusitar", "gemma2")
+        if args.design_beside is not None:
+            beside = tuple(b for b in args.design_beside.split(",") if b)
         sizes[name] = {"shape": z}
         for which in (args.design,) + beside:
             sizes[name][which] = design_point(which, z, min(args.steps, 50), max(3, args.warmup), clocks, pk)
@@ -581,8 +625,9 @@ def main() -> int:
     ap.add_argument("--skip-check", action="store_true", help="leave out the check of the timed logits against the 32-bit path")
     ap.add_argument("--breakdown", action="store_true",
                     help="instead of the JSON line: device time by kernel for one prefill step and one eager decode step")
-    ap.add_argument("--design", default=None, choices=["fusitar", "kofutar"],
+    ap.add_argument("--design", default=None, choices=["fusitar", "kofutar", "teluzen"],
                     help="instead of the default line: this design beside Gemma 2 (kofutar: beside Fusitar and Gemma 2) at equal sizes, prefill and decode, with each like kernel's roofline fraction")
+    ap.add_argument("--design-beside", default=None, help="which other designs run beside it (comma separated; empty: none); default: the closest ones")
     ap.add_argument("--design-sizes", default="s,m", help="which of the design sizes (s, m), comma separated")
     args = ap.parse_args()
 

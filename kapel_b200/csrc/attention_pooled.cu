@@ -233,6 +233,7 @@ pooled_attention_kernel(const PooledParams p) {
         }
         __syncthreads();
         const int sub = tid / PA_LPK, li = tid % PA_LPK;
+        const unsigned mates = ((1u << PA_LPK) - 1u) << (lane & ~(PA_LPK - 1));    // the lanes of this dot product: groups leave the loop at different times
         for (int item = sub; item < n * hq; item += PA_THREADS / PA_LPK) {
             const int j = item / hq, h = item - j * hq;
             const int g = h / group;
@@ -249,7 +250,7 @@ pooled_attention_kernel(const PooledParams p) {
                 for (int c = li; c < d; c += PA_LPK) dot = fmaf(Elem<T>::load(kp + c), qh[c], dot);
             }
 #pragma unroll
-            for (int o = PA_LPK / 2; o > 0; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
+            for (int o = PA_LPK / 2; o > 0; o >>= 1) dot += __shfl_xor_sync(mates, dot, o);
             if (li == 0) {
                 float s = dot * p.scale;
                 if (p.temp != nullptr) s *= p.temp[h];

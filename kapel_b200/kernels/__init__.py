@@ -1313,7 +1313,8 @@ def sample(logits: torch.Tensor, temperature: Optional[torch.Tensor] = None, uni
 _TIMED = ("embed", "rope_table", "rope_append", "glu", "cast", "gather_rows", "rmsnorm", "add_rmsnorm", "gemm",
           "paged_attention_rows", "paged_attention_mma", "sample", "proj_norm_append", "head_gate", "mlstm_scan", "moe_route",
           "moe_sort", "moe_grouped", "moe_combine", "gemm_glu_fused", "paged_attention_decode_fused", "layernorm", "concat2",
-          "head_norm_rope_append", "latent_append", "head_linear", "delta_scan", "latent_attention_mma")
+          "head_norm_rope_append", "latent_append", "head_linear", "delta_scan", "latent_attention_mma", "proj_rope_append",
+          "pool_blocks", "pooled_attention", "act")
 _timing = None
 _originals = {}
 
