@@ -29,6 +29,28 @@ typedef __nv_bfloat16 bf16;
 template <typename T> __device__ __forceinline__ float pooled_exp(float x) { return __expf(x); }
 template <> __device__ __forceinline__ float pooled_exp<float>(float x) { return expf(x); }
 
+// Eight neighbours of a row that starts on a 16-byte boundary, as 32-bit values.
+__device__ __forceinline__ void pooled_load8(const float* p, float (&x)[8]) {
+    const float4 a = *reinterpret_cast<const float4*>(p), b = *reinterpret_cast<const float4*>(p + 4);
+    x[0] = a.x; x[1] = a.y; x[2] = a.z; x[3] = a.w; x[4] = b.x; x[5] = b.y; x[6] = b.z; x[7] = b.w;
+}
+__device__ __forceinline__ void pooled_load8(const bf16* p, float (&x)[8]) {
+    const uint4 u = *reinterpret_cast<const uint4*>(p);
+    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&u);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const float2 f = __bfloat1622float2(h[i]);
+        x[2 * i] = f.x;
+        x[2 * i + 1] = f.y;
+    }
+}
+__device__ __forceinline__ float pooled_dot8(const float (&k)[8], const float* q, float acc) {
+    const float4 a = *reinterpret_cast<const float4*>(q), b = *reinterpret_cast<const float4*>(q + 4);
+    acc = fmaf(k[0], a.x, acc); acc = fmaf(k[1], a.y, acc); acc = fmaf(k[2], a.z, acc); acc = fmaf(k[3], a.w, acc);
+    acc = fmaf(k[4], b.x, acc); acc = fmaf(k[5], b.y, acc); acc = fmaf(k[6], b.z, acc); acc = fmaf(k[7], b.w, acc);
+    return acc;
+}
+
 // ------------------------------------------------------------------------------ proj_rope_append
 template <typename TS, typename TW, typename TO>
 __global__ void proj_rope_append_kernel(const Src<TS> src, int row_width, int q_off, int k_off, int v_off,
@@ -163,6 +185,7 @@ struct PooledParams {
     void* out;                 // [rows, hq, dv]
     float* stats;              // [rows, splits, hq, 2] (with splits > 1)
     float* partial;            // [rows, splits, hq, dv] (with splits > 1)
+    float* kept_scores;        // [rows, splits, hq, split_keys] (with splits > 1): the first walk's scores, which the second reads back
     long long slot_stride;
     int rows, hq, hkv, d, dv, page_size, table_width, n_pages, n_slots, max_blocks;
     int window, pool;          // window 0: every token is seen and no block; pool 0: no blocks
@@ -189,7 +212,7 @@ pooled_attention_kernel(const PooledParams p) {
     float* stalk = pm + (size_t)hq * PA_CHUNK;          // [hq][hq]
     float* sm = stalk + (size_t)hq * hq;                // [hq] maxima
     float* sz = sm + hq;                                // [hq] sums
-    long long* skey = reinterpret_cast<long long*>((reinterpret_cast<uintptr_t>(sz + hq) + 7) & ~(uintptr_t)7);   // [CHUNK] line of a token, or -1 - block
+    long long* skey = reinterpret_cast<long long*>((reinterpret_cast<uintptr_t>(sz + hq) + 7) & ~(uintptr_t)7);   // [CHUNK] a token's row of kv head 0 in the tables, or -1 - block
     const int r = blockIdx.x, z = blockIdx.y;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int count = p.row_count[r];
@@ -216,8 +239,10 @@ pooled_attention_kernel(const PooledParams p) {
     const T* vt = static_cast<const T*>(p.v_table);
     const int wide = d + dv;
 
-    // the scores of the keys [j0, j0 + n) into ss
-    auto scores = [&](int j0, int n) {
+    const bool vec = d % 8 == 0;                        // rows of keys start on 16-byte boundaries
+    const bool vec_means = vec && wide % 4 == 0;
+    // where the keys [j0, j0 + n) lie, into skey
+    auto keys_at = [&](int j0, int n) {
         for (int j = tid; j < n; j += PA_THREADS) {
             const int key = j0 + j;
             long long at;
@@ -227,11 +252,16 @@ pooled_attention_kernel(const PooledParams p) {
                 const int pos = first + (key - nb);
                 const int lp = pos / p.page_size;
                 const int page = lp < p.table_width ? p.block_table[(size_t)entry * p.table_width + lp] : -1;
-                at = (page >= 0 && page < p.n_pages) ? (long long)page * p.page_size + pos % p.page_size : (long long)0x7fffffffffffffffll;
+                // the token's row of kv head 0 in the tables [pages, kv heads, page size, .]: head g's lies g pages' lines further
+                at = (page >= 0 && page < p.n_pages) ? ((long long)page * p.hkv) * p.page_size + pos % p.page_size : (long long)0x7fffffffffffffffll;
             }
             skey[j] = at;
         }
         __syncthreads();
+    };
+    // the scores of the keys [j0, j0 + n) into ss
+    auto scores = [&](int j0, int n) {
+        keys_at(j0, n);
         const int sub = tid / PA_LPK, li = tid % PA_LPK;
         const unsigned mates = ((1u << PA_LPK) - 1u) << (lane & ~(PA_LPK - 1));    // the lanes of this dot product: groups leave the loop at different times
         for (int item = sub; item < n * hq; item += PA_THREADS / PA_LPK) {
@@ -244,10 +274,26 @@ pooled_attention_kernel(const PooledParams p) {
                 dot = 0.f;
             } else if (at < 0) {
                 const float* kp = pooled + ((size_t)(-1 - at) * p.hkv + g) * wide;
-                for (int c = li; c < d; c += PA_LPK) dot = fmaf(kp[c], qh[c], dot);
+                if (vec_means) {
+                    for (int c = li * 8; c < d; c += PA_LPK * 8) {
+                        float kx[8];
+                        pooled_load8(kp + c, kx);
+                        dot = pooled_dot8(kx, qh + c, dot);
+                    }
+                } else {
+                    for (int c = li; c < d; c += PA_LPK) dot = fmaf(kp[c], qh[c], dot);
+                }
             } else {
-                const T* kp = kt + kv_row(at, g, p.hkv, p.page_size) * d;
-                for (int c = li; c < d; c += PA_LPK) dot = fmaf(Elem<T>::load(kp + c), qh[c], dot);
+                const T* kp = kt + (size_t)(at + (long long)g * p.page_size) * d;
+                if (vec) {
+                    for (int c = li * 8; c < d; c += PA_LPK * 8) {
+                        float kx[8];
+                        pooled_load8(kp + c, kx);
+                        dot = pooled_dot8(kx, qh + c, dot);
+                    }
+                } else {
+                    for (int c = li; c < d; c += PA_LPK) dot = fmaf(Elem<T>::load(kp + c), qh[c], dot);
+                }
             }
 #pragma unroll
             for (int o = PA_LPK / 2; o > 0; o >>= 1) dot += __shfl_xor_sync(mates, dot, o);
@@ -280,6 +326,13 @@ pooled_attention_kernel(const PooledParams p) {
                     sm[h] = top;
                 }
             }
+            if (p.mode == 1) {
+                float* keep = p.kept_scores + ((size_t)r * p.splits + z) * hq * p.split_keys + (j0 - j_lo);
+                for (int i = tid; i < hq * n; i += PA_THREADS) {
+                    const int h = i / n, j = i - h * n;
+                    keep[(size_t)h * p.split_keys + j] = ss[h * PA_CHUNK + j];
+                }
+            }
             __syncthreads();
         }
         if (p.mode == 1) {
@@ -307,12 +360,24 @@ pooled_attention_kernel(const PooledParams p) {
     }
 
     // ---- the second walk: weights, normalised, mixed, times the values
-    float acc[OPT];
+    constexpr int ACC = OPT < 8 ? 8 : OPT;              // (eight neighbours a thread where the values' rows allow 16-byte loads)
+    const bool vec_values = dv % 8 == 0 && d % 4 == 0;
+    float acc[ACC];
 #pragma unroll
-    for (int u = 0; u < OPT; ++u) acc[u] = 0.f;
+    for (int u = 0; u < ACC; ++u) acc[u] = 0.f;
     for (int j0 = j_lo; j0 < j_hi; j0 += PA_CHUNK) {
         const int n = min(PA_CHUNK, j_hi - j0);
-        scores(j0, n);
+        if (p.mode == 2) {
+            keys_at(j0, n);
+            const float* keep = p.kept_scores + ((size_t)r * p.splits + z) * hq * p.split_keys + (j0 - j_lo);
+            for (int i = tid; i < hq * n; i += PA_THREADS) {
+                const int h = i / n, j = i - h * n;
+                ss[h * PA_CHUNK + j] = keep[(size_t)h * p.split_keys + j];
+            }
+            __syncthreads();
+        } else {
+            scores(j0, n);
+        }
         for (int i = tid; i < hq * n; i += PA_THREADS) {
             const int h = i / n, j = i - h * n;
             const float s = ss[h * PA_CHUNK + j];
@@ -326,6 +391,25 @@ pooled_attention_kernel(const PooledParams p) {
             pm[h * PA_CHUNK + j] = w;
         }
         __syncthreads();
+        if (vec_values) {
+#pragma unroll
+            for (int u8 = 0; u8 < ACC / 8; ++u8) {
+                const int o = (tid + u8 * PA_THREADS) * 8;
+                if (o >= hq * dv) break;
+                const int h = o / dv, c = o - h * dv;
+                const int g = h / group;
+                for (int j = 0; j < n; ++j) {
+                    const long long at = skey[j];
+                    if (at == 0x7fffffffffffffffll) continue;
+                    float vx[8];
+                    if (at < 0) pooled_load8(pooled + ((size_t)(-1 - at) * p.hkv + g) * wide + d + c, vx);
+                    else pooled_load8(vt + (size_t)(at + (long long)g * p.page_size) * dv + c, vx);
+                    const float w = pm[h * PA_CHUNK + j];
+#pragma unroll
+                    for (int k = 0; k < 8; ++k) acc[u8 * 8 + k] = fmaf(w, vx[k], acc[u8 * 8 + k]);
+                }
+            }
+        } else
 #pragma unroll
         for (int u = 0; u < OPT; ++u) {
             const int o = tid + u * PA_THREADS;
@@ -337,7 +421,7 @@ pooled_attention_kernel(const PooledParams p) {
                 const long long at = skey[j];
                 if (at == 0x7fffffffffffffffll) continue;
                 const float v = at < 0 ? pooled[((size_t)(-1 - at) * p.hkv + g) * wide + d + c]
-                                       : Elem<T>::load(vt + kv_row(at, g, p.hkv, p.page_size) * dv + c);
+                                       : Elem<T>::load(vt + (size_t)(at + (long long)g * p.page_size) * dv + c);
                 a = fmaf(pm[h * PA_CHUNK + j], v, a);
             }
             acc[u] = a;
@@ -345,6 +429,16 @@ pooled_attention_kernel(const PooledParams p) {
         __syncthreads();
     }
     if (n_keys <= 0 && p.mode == 0) return;                 // zeros were written above
+    if (vec_values) {
+#pragma unroll
+        for (int u = 0; u < ACC; ++u) {
+            const int o = (tid + (u >> 3) * PA_THREADS) * 8 + (u & 7);
+            if (o >= hq * dv) break;
+            if (p.mode == 0) Elem<T>::store(out + (size_t)r * hq * dv + o, acc[u]);
+            else p.partial[((size_t)r * p.splits + z) * hq * dv + o] = acc[u];
+        }
+        return;
+    }
 #pragma unroll
     for (int u = 0; u < OPT; ++u) {
         const int o = tid + u * PA_THREADS;
@@ -469,8 +563,8 @@ extern "C" int kb_pool_blocks(const void* k_table, const void* v_table, int dt, 
 }
 
 // Scratch floats for `splits` slices of the keys (0 with one).
-extern "C" long long kb_pooled_attention_scratch_floats(int rows, int hq, int dv, int splits) {
-    return splits > 1 ? (long long)rows * splits * hq * (dv + 2) : 0;
+extern "C" long long kb_pooled_attention_scratch_floats(int rows, int hq, int dv, int splits, int split_keys) {
+    return splits > 1 ? (long long)rows * splits * hq * (dv + 2 + split_keys) : 0;
 }
 
 extern "C" int kb_pooled_attention(void* out, const void* q, const void* k_table, const void* v_table, int dt, const float* pooled,
@@ -490,6 +584,7 @@ extern "C" int kb_pooled_attention(void* out, const void* q, const void* k_table
     p.q = q; p.k_table = k_table; p.v_table = v_table; p.pooled = pooled; p.block_table = block_table; p.row_entry = row_entry;
     p.row_count = row_count; p.slots = slots; p.talk = talk; p.temp = temp; p.out = out;
     p.stats = scratch; p.partial = scratch != nullptr ? scratch + (size_t)rows * splits * hq * 2 : nullptr;
+    p.kept_scores = scratch != nullptr ? p.partial + (size_t)rows * splits * hq * dv : nullptr;
     p.slot_stride = slot_stride; p.rows = rows; p.hq = hq; p.hkv = hkv; p.d = d; p.dv = dv; p.page_size = page_size;
     p.table_width = table_width; p.n_pages = n_pages; p.n_slots = n_slots; p.max_blocks = max_blocks; p.window = window;
     p.pool = pool; p.splits = splits; p.split_keys = split_keys; p.mode = 0; p.scale = scale;

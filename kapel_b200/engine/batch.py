@@ -265,6 +265,26 @@ class StepBatch:
             self.memo[key] = pooled_slices(self.plan.rows, longest, window, pool, sm_count(self.ids.device), K.pooled_attention_chunk())
         return self.memo[key]
 
+    def pooled_tiles(self):
+        """(tile_entry, tile_row0, tile_nq) on the device for the tensor-core kernel of the attention over
+        a window and pooled blocks: each request's rows in runs of that kernel's tile. None in a step
+        where every request brings one token (the kernel that cuts the keys into slices takes those)."""
+        key = "pooled_tiles"
+        if key not in self.memo:
+            from .. import kernels as K
+
+            plan = self.plan
+            if not len(plan.q_len) or int(plan.q_len.max()) <= 1 or not self.ids.is_cuda:
+                self.memo[key] = None
+            else:
+                arrays = cut_tiles(plan.q_start, plan.q_len, K.pooled_attention_tile_rows())
+                n = arrays[0].size
+                host = torch.from_numpy(np.concatenate(arrays)).pin_memory()
+                dev = host.to(self.ids.device, non_blocking=True)
+                self.memo[key] = (dev[:n], dev[n : 2 * n], dev[2 * n :], host)
+        tiles = self.memo[key]
+        return tiles[:3] if tiles is not None else None
+
     def longest_portion(self) -> int:
         """The most rows any request brings in this step (what sizes a launch of a block a run of a request's rows)."""
         return int(self.plan.q_len.max()) if len(self.plan.q_len) else 0

@@ -142,5 +142,5 @@ def write_safetensors(path, tensors: Dict[str, torch.Tensor], metadata=None) -> 
             t = tensors[name].detach().contiguous().cpu()
             if t.numel() == 0:
                 continue
-            raw = t.view(torch.uint8) if t.dtype != torch.bool else t.to(torch.uint8)
+            raw = t.reshape(-1).view(torch.uint8) if t.dtype != torch.bool else t.to(torch.uint8)      # (a tensor of no dimensions has no last one to view as bytes)
             f.write(memoryview(raw.reshape(-1).numpy()))

@@ -36,7 +36,13 @@ TELUZEN_C = {"architecture": "Teluzen", "vocab": 64, "width": 32, "max_positions
     layer(2, 2, 16, 8, 0.25, 1000, 8, {"base": 1e6, "dims": 8, "scaling": {"factor": 8.0, "original": 128, "fast": 16.0, "slow": 1.0}}, False, moe(8, 6, 3, 8)),
     layer(8, 4, 8, 4, 0.35, 64, 64, None, True, None),
 ]}
-CONFIGS = {"A": (TELUZEN_A, 31), "B": (TELUZEN_B, 32), "C": (TELUZEN_C, 33)}
+# D: head and value sizes in multiples of 16, which in bfloat16 send prompt portions to the tensor-core kernel.
+TELUZEN_D = {"architecture": "Teluzen", "vocab": 97, "width": 64, "max_positions": 512, "norm": {"eps": 1e-5}, "layers": [
+    layer(4, 2, 32, 16, 0.2, 24, 4, {"base": 2000.0, "dims": 16}, False, {"kind": "dense", "ff": 32}),
+    layer(8, 2, 16, 32, 0.3, 40, 8, {"base": 1000.0, "dims": 8, "scaling": SCALED}, True, moe(16, 4, 2, 8)),
+    layer(4, 2, 16, 32, 0.25, 9, 2, None, True, None),
+]}
+CONFIGS = {"A": (TELUZEN_A, 31), "B": (TELUZEN_B, 32), "C": (TELUZEN_C, 33), "D": (TELUZEN_D, 34)}
 # Largest difference of logits over the largest plain logit, row by row. The 32-bit runs see about 1e-5 and
 # every row is held to 1e-4. In bfloat16 (products and caches in bfloat16 under 32-bit norms, scores, weights
 # and residual) the median row is held under 3e-2, at most one row in twenty may pass 1e-1 and none 3e-1: a
@@ -307,13 +313,51 @@ def test_window_and_pooled_blocks_in_one_softmax_with_mixed_heads(hq, hkv, d, dv
     assert torch.isnan(pr.means[0]).all()
     entry, _, count, _ = pr.rows(spans)
     q = dev(np.concatenate(qs), dtype)
-    for splits, keys in ((1, 0), (2, 64), (3, 64)):
+    for splits, keys in ((1, 0), (2, 128), (3, 64)):                                    # slices that hold the longest row's keys (150 with blocks of one token)
         got = K.pooled_attention(q, pr.kt, pr.vt, pr.means, pr.table, entry, count, pr.slots, dev(talk), dev(temp), 16, size, pool, scale, splits, keys)
         assert rel_err(got.float().cpu().numpy(), want) < tol, (splits, keys)
     # without a mix and without numbers of the heads the same kernel is plain attention over window and blocks
     got = K.pooled_attention(q, pr.kt, pr.vt, pr.means, pr.table, entry, count, pr.slots, None, None, 16, size, pool, scale)
     want = np.concatenate([plain_attention(q_, k, v, np.eye(hq), np.ones(hq), scale, size, pool) for q_, k, v in zip(qs, ks, vs)])
     assert rel_err(got.float().cpu().numpy(), want) < tol
+
+
+@pytest.mark.parametrize("hq,hkv,d,dv,size,pool", [(8, 1, 64, 64, 64, 8), (2, 1, 96, 48, 96, 8), (16, 4, 32, 32, 40, 4), (12, 4, 16, 16, 9, 3),
+                                                    (32, 8, 16, 16, 20, 2), (8, 8, 32, 48, 24, 8), (3, 3, 16, 128, 7, 16), (16, 4, 128, 128, 50, 1),
+                                                    (5, 1, 48, 80, 1, 1), (4, 2, 16, 16, 1000, 4)])
+def test_tiles_of_tokens_with_all_heads_on_tensor_cores(hq, hkv, d, dv, size, pool):
+    """The kernel for prompt portions: tiles of 16 tokens with all heads, two walks over the keys, the mix in
+    registers. One launch holds a portion that starts deep in a sequence (earlier rows lie in the cache only),
+    a whole short prompt, a single token, and a portion that starts one token before a tile would; also without
+    a mix and without numbers of the heads."""
+    from kapel_b200 import kernels as K
+    from kapel_b200.engine.batch import cut_tiles
+
+    assert K.pooled_attention_tiled(hq, hkv, d, dv)
+    rng = np.random.default_rng(hq * 77 + size)
+    lengths = (150, 61, 90, 131)
+    spans = [(0, 100, 150), (1, 0, 61), (2, 89, 90), (3, 15, 131)]
+    qs = [bf16_round(rng.standard_normal((n, hq, d))) for n in lengths]
+    ks = [bf16_round(rng.standard_normal((n, hkv, d))) for n in lengths]
+    vs = [bf16_round(rng.standard_normal((n, hkv, dv))) for n in lengths]
+    talk, temp = rng.standard_normal((hq, hq)) / np.sqrt(hq), rng.standard_normal(hq) + 1.0
+    talk, temp = dev(talk).cpu().double().numpy(), dev(temp).cpu().double().numpy()
+    scale = 0.9 / np.sqrt(d)
+    pr = PagedRequests(rng, ks, vs, torch.bfloat16, pool, max(lengths) // pool + 1)
+    pr.take_means([(e, 0, n) for e, n in enumerate(lengths)])
+    entry, _, count, _ = pr.rows(spans)
+    q = dev(np.concatenate([qs[e][a:b] for e, a, b in spans]), torch.bfloat16)
+    q_len = np.asarray([b - a for _, a, b in spans])
+    tiles = tuple(dev(t, torch.int32) for t in cut_tiles(np.cumsum(q_len) - q_len, q_len, K.pooled_attention_tile_rows()))
+    for mix in (True, False):
+        t_, m_ = (talk, temp) if mix else (np.eye(hq), np.ones(hq))
+        want = np.concatenate([plain_attention(qs[e], ks[e], vs[e], t_, m_, scale, size, pool)[a:b] for e, a, b in spans])
+        got = K.pooled_attention(q, pr.kt, pr.vt, pr.means, pr.table, entry, count, pr.slots, dev(t_) if mix else None, dev(m_) if mix else None,
+                                 16, size, pool, scale, tiles=tiles)
+        rows = K.pooled_attention(q, pr.kt, pr.vt, pr.means, pr.table, entry, count, pr.slots, dev(t_) if mix else None, dev(m_) if mix else None,
+                                  16, size, pool, scale)
+        assert rel_err(got.float().cpu().numpy(), want) < 1.5e-2, mix
+        assert rel_err(got.float().cpu().numpy(), rows.float().cpu().numpy()) < 1.5e-2, mix
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
@@ -334,6 +378,7 @@ def test_one_loud_key_is_seen_in_the_window_lost_below_it_and_found_again_in_its
     k[at, 0] = 16.0 * pool * u                                                           # its block's mean still scores 16 * 4 * scale
     q = 0.05 * rng.standard_normal((T, H, d)) + 4.0 * u
     v = rng.standard_normal((T, G, dv))
+    v[at, 0] = 12.0 * pool                                                               # its value stands out of the quiet ones, also as a share of its block's mean
     if dtype == torch.bfloat16:
         q, k, v = bf16_round(q), bf16_round(k), bf16_round(v)
     talk, temp = np.eye(H), np.ones(H)
@@ -351,7 +396,7 @@ def test_one_loud_key_is_seen_in_the_window_lost_below_it_and_found_again_in_its
     for i in (at, at + size - 1):                                                        # the first and the last query with the key in the window
         assert np.abs(got[i] - v[at, 0]).max() < 3 * tol * np.abs(v).max(), i
     for i in range(at + size, first_as_block):                                           # out of the window, its block not whole below it
-        assert np.abs(got[i] - v[at, 0]).max() > 0.3 and np.abs(got[i] - mean).max() > 0.3, i
+        assert np.abs(got[i]).max() < 4.0, i                                             # a mean of quiet values: nothing of the loud one
     for i in (first_as_block, first_as_block + 1, first_as_block + 400):
         if i < T:
             assert np.abs(got[i] - mean).max() < 3 * tol * np.abs(v).max(), i
@@ -445,7 +490,7 @@ def test_cache_pages_hold_the_window_and_a_slot_holds_the_block_means(models):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["A", "B", "C"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D"])
 def test_whole_prompts_portions_and_decoding_against_plain(models, name, dtype):
     """A prompt whole; the same prompt in portions of changing size down to two tokens and then token by
     token: 70 decoded tokens pass over every window's and block's edge and over pages; logits at every position."""
@@ -498,7 +543,7 @@ def test_the_residual_after_every_layer_against_plain(models):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["A", "B", "C"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D"])
 def test_mixed_batches_and_reused_pages_and_slots_against_each_alone(models, name, dtype):
     """Up to four unequal requests a step, portions beside single tokens, a request left out of a step,
     requests that end and whose pages and slots (with the block means the last owner left there) the next
@@ -559,7 +604,7 @@ def test_recorded_passes_give_what_eager_ones_give(models):
 
 ODD = {"architecture": "Teluzen", "vocab": 77, "width": 52, "max_positions": 300, "norm": {"eps": 1e-6}, "layers": [
     layer(3, 1, 12, 10, 0.3, 9, 7, {"base": 80.0, "dims": 6, "scaling": SCALED}, True, {"kind": "dense", "ff": 13}),
-    layer(5, 5, 6, 2, 0.5, 11, 2, {"base": 7.0, "dims": 6}, True, moe(11, 3, 2, 5))]}
+    layer(5, 1, 6, 10, 0.5, 11, 2, {"base": 7.0, "dims": 6}, True, moe(11, 3, 2, 5))]}
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
