@@ -10,6 +10,10 @@
 //           maximum and sum; a thread holds all heads' weights of its (token, key) pairs in registers,
 //           mixes them for the block's output heads and leaves them in shared memory as bfloat16;
 //           each warp multiplies one output head's mixed weights with its kv head's values.
+// Where scratch memory allows, the first launch also keeps its (masked) scores, and the second launch is
+// `pooled_mix_kernel` instead: a block (tile, 8 or 16 output heads) fetches a step's scores of all heads by
+// cp.async, with the values of its heads' kv heads, and normalises, mixes and multiplies: no queries, no
+// keys, no score computed twice.
 // Keys and values of a step lie in shared memory for all kv heads (the pooled means, 32-bit in their
 // table, are rounded to bfloat16 on the way in); fragments come by ldmatrix. Which keys a token sees:
 // the blocks b < floor((c - window) / pool) and the tokens [max(0, c - window), c), c the positions it
@@ -41,10 +45,13 @@ struct PooledMmaParams {
     const float* temp;         // [hq] or null
     bf16* out;                 // [rows, hq, dv]
     float* stats;              // [rows, hq, 2]
+    float* kept;               // [tiles, kept_steps, hq, 16, keys a step] the first launch's scores (-inf: not seen), or null
+    int kept_steps;            // steps a tile has room for
     long long slot_stride;
     int hq, hkv, d, dv, page_size, table_width, n_pages, n_slots, max_blocks;
     int window, pool;
     int ncv;                   // the most kv heads any block's output heads read values of
+    int ncv_mix;               // the same for the blocks of the launch that reads kept scores (8 or 16 heads a block)
     int mode;
     float scale;
 };
@@ -252,6 +259,7 @@ pooled_mma_kernel(const PooledMmaParams p) {
         const bf16* bV = sV + (size_t)buf * p.ncv * NK * ldv;
         // ---- scores: an item is a head and 16 keys
         constexpr int NSUB = NK / 16;
+        float* keep = (p.mode == 1 && p.kept != nullptr) ? p.kept + ((size_t)t * p.kept_steps + j0 / NK) * hq * PM_ROWS * NK : nullptr;
         for (int item = warp; item < hq * NSUB; item += PM_WARPS) {
             const int g = item / NSUB, sub = item - g * NSUB;
             const int c = g / group;
@@ -292,6 +300,12 @@ pooled_mma_kernel(const PooledMmaParams p) {
                     }
                     sa[nt * 8 + e] = va;
                     sb[nt * 8 + e] = vb;
+                    if (e == 1 && keep != nullptr) {         // the pair (e = 0, 1) of neighbouring keys in one store
+                        float* ka = keep + (size_t)(g * PM_ROWS + ia) * NK + sub * 16 + (lane & 3) * 2 + nt * 8;
+                        float* kb2 = keep + (size_t)(g * PM_ROWS + ib) * NK + sub * 16 + (lane & 3) * 2 + nt * 8;
+                        *reinterpret_cast<float2*>(ka) = make_float2(sa[nt * 8], va);
+                        *reinterpret_cast<float2*>(kb2) = make_float2(sb[nt * 8], vb);
+                    }
                 }
         }
         __syncthreads();
@@ -382,12 +396,207 @@ pooled_mma_kernel(const PooledMmaParams p) {
     }
 }
 
+// The second launch when the first kept its scores: a block (tile, 8 output heads) fetches a step's scores of all
+// heads (cp.async straight into shared memory, two buffers) and the values of its heads' kv heads, normalises,
+// mixes and multiplies as above. No queries, no keys, no score is computed twice.
+struct PmMixLayout { unsigned sc, v, pp, m, il, talk, ints, total; };
+
+__host__ __device__ inline PmMixLayout pm_mix_layout(int hq, int dv, int ncv, int nk, int hb) {
+    PmMixLayout L;
+    unsigned at = 0;
+    L.sc = pm_take(at, (size_t)2 * hq * PM_ROWS * (nk + 4) * 4);
+    L.v = pm_take(at, (size_t)2 * ncv * nk * (dv + PM_PAD) * 2);
+    L.pp = pm_take(at, (size_t)hb * PM_ROWS * (nk + PM_PAD) * 2);
+    L.m = pm_take(at, (size_t)hq * PM_ROWS * 4);
+    L.il = pm_take(at, (size_t)hq * PM_ROWS * 4);
+    L.talk = pm_take(at, (size_t)hb * 32 * 4);
+    L.ints = pm_take(at, (size_t)3 * PM_ROWS * 4);
+    L.total = at;
+    return L;
+}
+
+// HB: output heads a block, 8 (two warps a head, halves of the values) or 16 (a warp a head).
+template <int NK, int HMAX, int DVMAX, int HB>
+__global__ void __launch_bounds__(PM_THREADS, 1)
+pooled_mix_kernel(const PooledMmaParams p) {
+    extern __shared__ __align__(16) unsigned char pm_smem[];
+    const int hq = p.hq, hkv = p.hkv, d = p.d, dv = p.dv, group = p.hq / p.hkv;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int t = gridDim.x - 1 - blockIdx.x;
+    const int entry = p.tile_entry[t], r0 = p.tile_row0[t], nq = min(p.tile_nq[t], PM_ROWS);
+    constexpr int SPLIT = PM_WARPS / HB;                  // warps an output head
+    const int h0 = blockIdx.y * HB;
+    const int nh = min(HB, hq - h0);
+    const int c_lo = h0 / group;
+    const int ncv = (h0 + nh - 1) / group - c_lo + 1;
+    const PmMixLayout L = pm_mix_layout(hq, dv, p.ncv_mix, NK, HB);
+    float* sc = reinterpret_cast<float*>(pm_smem + L.sc);
+    bf16* sV = reinterpret_cast<bf16*>(pm_smem + L.v);
+    bf16* pp = reinterpret_cast<bf16*>(pm_smem + L.pp);
+    float* s_m = reinterpret_cast<float*>(pm_smem + L.m);
+    float* s_il = reinterpret_cast<float*>(pm_smem + L.il);
+    float* s_talk = reinterpret_cast<float*>(pm_smem + L.talk);
+    int* s_cnt = reinterpret_cast<int*>(pm_smem + L.ints);
+    int* s_first = s_cnt + PM_ROWS;
+    int* s_nb = s_first + PM_ROWS;
+    constexpr int LDC = NK + 4;                           // 16-byte rows for the copies; the mix reads along a row
+    const int ldv = dv + PM_PAD, ldp = NK + PM_PAD;
+    const int wide = d + dv;
+    const uint4 zero4 = make_uint4(0u, 0u, 0u, 0u);
+
+    if (tid < PM_ROWS) {
+        int c = tid < nq ? p.row_count[r0 + tid] : 0;
+        c = max(c, 0);
+        const bool past = p.window > 0 && c > p.window;
+        s_cnt[tid] = c;
+        s_first[tid] = past ? c - p.window : 0;
+        s_nb[tid] = (past && p.pool > 0) ? min((c - p.window) / p.pool, p.max_blocks) : 0;
+    }
+    for (int i = tid; i < nh * HMAX; i += PM_THREADS) {
+        const int h = h0 + i / HMAX, g = i % HMAX;
+        s_talk[i] = g >= hq ? 0.f : (p.talk != nullptr ? p.talk[(size_t)h * hq + g] : (h == g ? 1.f : 0.f));
+    }
+    for (int i = tid; i < hq * PM_ROWS; i += PM_THREADS) {
+        const int g = i / PM_ROWS, r = i - g * PM_ROWS;
+        float m = 0.f, il = 0.f;
+        if (r < nq) {
+            const float* st = p.stats + ((size_t)(r0 + r) * hq + g) * 2;
+            m = st[0];
+            il = st[1] > 0.f ? 1.f / st[1] : 0.f;
+        }
+        s_m[i] = m;
+        s_il[i] = il;
+    }
+    __syncthreads();
+    int nb_max = 0, first_min = 0x7fffffff, c_max = 0;
+    for (int i = 0; i < nq; ++i) {
+        nb_max = max(nb_max, s_nb[i]);
+        first_min = min(first_min, s_first[i]);
+        c_max = max(c_max, s_cnt[i]);
+    }
+    const int n_keys = c_max > 0 ? nb_max + (c_max - first_min) : 0;
+    const int slot = p.slots[entry];
+    const float* pooled = p.pooled + (size_t)((slot > 0 && slot < p.n_slots) ? slot : 0) * p.slot_stride;
+    const int* pages = p.block_table + (size_t)entry * p.table_width;
+
+    constexpr int OT = (DVMAX / 16 + SPLIT - 1) / SPLIT;   // 16-wide value tiles a warp
+    float o[2 * OT][4];
+#pragma unroll
+    for (int n = 0; n < 2 * OT; ++n) o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f;
+
+    constexpr int TPK = PM_THREADS / NK;
+    auto issue = [&](int j0, int buf) {
+        // the step's scores: rows of NK floats, [hq * 16] of them
+        const float* from = p.kept + ((size_t)t * p.kept_steps + j0 / NK) * hq * PM_ROWS * NK;
+        float* to = sc + (size_t)buf * hq * PM_ROWS * LDC;
+        for (int idx = tid; idx < hq * PM_ROWS * (NK / 4); idx += PM_THREADS) {
+            const int row = idx / (NK / 4), ch = idx - row * (NK / 4);
+            pm_cp_async16(to + (size_t)row * LDC + ch * 4, from + (size_t)row * NK + ch * 4);
+        }
+        const int jj = tid / TPK, sub = tid - jj * TPK;
+        const int j = j0 + jj;
+        bf16* vd = sV + (size_t)buf * p.ncv_mix * NK * ldv + (size_t)jj * ldv;
+        long long row = -1;
+        if (j >= nb_max && j < n_keys) {
+            const int pos = first_min + (j - nb_max);
+            const int lp = pos / p.page_size;
+            const int page = lp < p.table_width ? pages[lp] : -1;
+            if (page >= 0 && page < p.n_pages) row = (long long)page * hkv * p.page_size + (pos - lp * p.page_size);
+        }
+        if (row >= 0) {
+            for (int cl = 0; cl < ncv; ++cl) {
+                const bf16* src = p.v_table + (size_t)(row + (long long)(c_lo + cl) * p.page_size) * dv;
+                for (int ch = sub; ch * 8 < dv; ch += TPK) pm_cp_async16(vd + (size_t)cl * NK * ldv + ch * 8, src + ch * 8);
+            }
+        } else if (j < nb_max) {
+            for (int cl = 0; cl < ncv; ++cl) {
+                const float* src = pooled + ((size_t)j * hkv + c_lo + cl) * wide + d;
+                for (int ch = sub; ch * 8 < dv; ch += TPK) {
+                    const float4 a = *reinterpret_cast<const float4*>(src + ch * 8), b = *reinterpret_cast<const float4*>(src + ch * 8 + 4);
+                    *reinterpret_cast<uint4*>(vd + (size_t)cl * NK * ldv + ch * 8) = make_uint4(pm_pack(a.x, a.y), pm_pack(a.z, a.w), pm_pack(b.x, b.y), pm_pack(b.z, b.w));
+                }
+            }
+        } else {
+            for (int cl = 0; cl < ncv; ++cl)
+                for (int ch = sub; ch * 8 < dv; ch += TPK) *reinterpret_cast<uint4*>(vd + (size_t)cl * NK * ldv + ch * 8) = zero4;
+        }
+        pm_cp_async_commit();
+    };
+
+    if (n_keys > 0) issue(0, 0);
+    for (int j0 = 0; j0 < n_keys; j0 += NK) {
+        const int buf = (j0 / NK) & 1;
+        pm_cp_async_wait_all();
+        __syncthreads();                                     // the step's scores and values are in; everyone has left the step before
+        if (j0 + NK < n_keys) issue(j0 + NK, buf ^ 1);
+        const float* bS = sc + (size_t)buf * hq * PM_ROWS * LDC;
+        const bf16* bV = sV + (size_t)buf * p.ncv_mix * NK * ldv;
+        for (int e = tid; e < PM_ROWS * NK; e += PM_THREADS) {
+            const int i = e / NK, jj = e - i * NK;
+            float pg[HMAX];
+#pragma unroll
+            for (int g = 0; g < HMAX; ++g) {
+                pg[g] = 0.f;
+                if (g < hq) {
+                    const float v = bS[(size_t)(g * PM_ROWS + i) * LDC + jj];
+                    pg[g] = v == -INFINITY ? 0.f : __expf(v - s_m[g * PM_ROWS + i]) * s_il[g * PM_ROWS + i];
+                }
+            }
+            for (int hl = 0; hl < nh; ++hl) {
+                const float4* tr = reinterpret_cast<const float4*>(s_talk + hl * HMAX);
+                float w = 0.f;
+#pragma unroll
+                for (int g4 = 0; g4 < HMAX / 4; ++g4) {
+                    const float4 t4 = tr[g4];
+                    w = fmaf(t4.x, pg[4 * g4], w); w = fmaf(t4.y, pg[4 * g4 + 1], w);
+                    w = fmaf(t4.z, pg[4 * g4 + 2], w); w = fmaf(t4.w, pg[4 * g4 + 3], w);
+                }
+                pp[(size_t)(hl * PM_ROWS + i) * ldp + jj] = __float2bfloat16(w);
+            }
+        }
+        __syncthreads();
+        if (warp < SPLIT * nh) {
+            const int hl = warp / SPLIT, half = warp % SPLIT;
+            const int cl = (h0 + hl) / group - c_lo;
+            const bf16* pa = pp + (size_t)(hl * PM_ROWS + (lane & 15)) * ldp + (lane >> 4) * 8;
+            const bf16* vf = bV + ((size_t)cl * NK + (lane & 7) + ((lane >> 3) & 1) * 8) * ldv + (lane >> 4) * 8 + half * OT * 16;
+#pragma unroll
+            for (int kk = 0; kk < NK; kk += 16) {
+                uint32_t a[4];
+                pm_ldmatrix_x4(a, pa + kk);
+#pragma unroll
+                for (int n2 = 0; n2 < OT; ++n2) {
+                    if ((half * OT + n2) * 16 < dv) {
+                        uint32_t b[4];
+                        pm_ldmatrix_x4_trans(b, vf + (size_t)kk * ldv + n2 * 16);
+                        pm_mma(o[2 * n2], a, b[0], b[1]);
+                        pm_mma(o[2 * n2 + 1], a, b[2], b[3]);
+                    }
+                }
+            }
+        }
+        // (the next step's first barrier stands between these reads of pp and its writes)
+    }
+    if (warp < SPLIT * nh) {
+        const int h = h0 + warp / SPLIT, half = warp % SPLIT;
+#pragma unroll
+        for (int n = 0; n < 2 * OT; ++n) {
+            const int col = (half * OT * 2 + n) * 8 + (lane & 3) * 2;
+            if (col < dv) {
+                const int i = lane >> 2;
+                if (i < nq) *reinterpret_cast<uint32_t*>(p.out + ((size_t)(r0 + i) * hq + h) * dv + col) = pm_pack(o[n][0], o[n][1]);
+                if (i + 8 < nq) *reinterpret_cast<uint32_t*>(p.out + ((size_t)(r0 + i + 8) * hq + h) * dv + col) = pm_pack(o[n][2], o[n][3]);
+            }
+        }
+    }
+}
+
 // The most kv heads whose values any block of PM_HEADS output heads reads.
-static int pm_value_heads(int hq, int hkv) {
+static int pm_value_heads(int hq, int hkv, int hb = PM_HEADS) {
     const int group = hq / hkv;
     int most = 1;
-    for (int h0 = 0; h0 < hq; h0 += PM_HEADS) {
-        const int last = (h0 + PM_HEADS < hq ? h0 + PM_HEADS : hq) - 1;
+    for (int h0 = 0; h0 < hq; h0 += hb) {
+        const int last = (h0 + hb < hq ? h0 + hb : hq) - 1;
         const int n = last / group - h0 / group + 1;
         if (n > most) most = n;
     }
@@ -395,6 +604,9 @@ static int pm_value_heads(int hq, int hkv) {
 }
 
 constexpr unsigned PM_SMEM_LIMIT = 227 * 1024;
+
+// Output heads a block of the launch that reads kept scores.
+static int pm_mix_heads(int hq) { return hq > PM_HEADS ? 16 : 8; }
 
 // How the kernel runs these sizes: keys a step * 4 + stages, the first of (32, 2), (16, 2), (32, 1), (16, 1)
 // that fits shared memory; 0 if the kernel does not take the sizes.
@@ -415,6 +627,18 @@ static int pm_launch(PooledMmaParams p, int tiles, cudaStream_t s) {
     pooled_mma_kernel<NK, HMAX, DVMAX, STAGES><<<dim3(tiles, 1), PM_THREADS, smem, s>>>(p);
     if (int e = check_launch("pooled_attention_mma statistics")) return e;
     p.mode = 2;
+    if (p.kept != nullptr) {
+        if (pm_mix_heads(p.hq) == 16) {
+            const unsigned mix_smem = pm_mix_layout(p.hq, p.dv, p.ncv_mix, NK, 16).total;
+            if (mix_smem > 48 * 1024) cudaFuncSetAttribute(pooled_mix_kernel<NK, HMAX, DVMAX, 16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)mix_smem);
+            pooled_mix_kernel<NK, HMAX, DVMAX, 16><<<dim3(tiles, (p.hq + 15) / 16), PM_THREADS, mix_smem, s>>>(p);
+        } else {
+            const unsigned mix_smem = pm_mix_layout(p.hq, p.dv, p.ncv_mix, NK, 8).total;
+            if (mix_smem > 48 * 1024) cudaFuncSetAttribute(pooled_mix_kernel<NK, HMAX, DVMAX, 8>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)mix_smem);
+            pooled_mix_kernel<NK, HMAX, DVMAX, 8><<<dim3(tiles, 1), PM_THREADS, mix_smem, s>>>(p);
+        }
+        return check_launch("pooled_attention_mma mix");
+    }
     pooled_mma_kernel<NK, HMAX, DVMAX, STAGES><<<dim3(tiles, (p.hq + PM_HEADS - 1) / PM_HEADS), PM_THREADS, smem, s>>>(p);
     return check_launch("pooled_attention_mma");
 }
@@ -442,12 +666,31 @@ extern "C" int kb_pooled_attention_mma_tile_rows() { return PM_ROWS; }
 
 extern "C" long long kb_pooled_attention_mma_scratch_floats(int rows, int hq) { return (long long)rows * hq * 2; }
 
+// Steps a tile needs room for when the first launch keeps its scores for the second: the most keys a tile of a
+// request that has seen `longest` positions reads, over the keys a step.
+static int pm_kept_steps(int nk, int window, int pool, int max_blocks, int longest) {
+    long long tokens = window > 0 ? (longest < window + PM_ROWS - 1 ? longest : window + PM_ROWS - 1) : longest;
+    long long blocks = (window > 0 && pool > 0 && longest > window) ? (longest - window) / pool : 0;
+    if (blocks > max_blocks) blocks = max_blocks;
+    return (int)((tokens + blocks + nk - 1) / nk);
+}
+
+// Floats of scratch memory for the kept scores (0: these sizes are not taken).
+extern "C" long long kb_pooled_attention_mma_kept_floats(int tiles, int hq, int hkv, int d, int dv, int window, int pool, int max_blocks,
+                                                         int longest) {
+    const int form = pm_form(hq, hkv, d, dv);
+    if (form <= 0 || tiles <= 0 || longest <= 0) return 0;
+    const int nk = form / 4;
+    if (pm_mix_layout(hq, dv, pm_value_heads(hq, hkv, pm_mix_heads(hq)), nk, pm_mix_heads(hq)).total > PM_SMEM_LIMIT) return 0;
+    return (long long)tiles * pm_kept_steps(nk, window, pool, pool > 0 ? max_blocks : 0, longest) * hq * PM_ROWS * nk;
+}
+
 extern "C" int kb_pooled_attention_mma(void* out, const void* q, const void* k_table, const void* v_table, const float* pooled,
                                        long long slot_stride, int n_slots, int max_blocks, const int* block_table,
                                        const int* row_count, const int* tile_entry, const int* tile_row0, const int* tile_nq,
                                        int tiles, const int* slots, const float* talk, const float* temp, int rows, int hq, int hkv,
                                        int d, int dv, int page_size, int table_width, int n_pages, int window, int pool, float scale,
-                                       float* scratch, void* stream) {
+                                       float* scratch, float* kept, int longest, void* stream) {
     KB_REQUIRE(rows >= 0 && tiles >= 0 && hq > 0 && hkv > 0 && hq % hkv == 0, "pooled_attention_mma: rows %d, tiles %d, %d heads over %d", rows, tiles, hq, hkv);
     const int form = pm_form(hq, hkv, d, dv);
     KB_REQUIRE(form > 0, "pooled_attention_mma: %d heads over %d of sizes %d / %d are not taken", hq, hkv, d, dv);
@@ -464,6 +707,10 @@ extern "C" int kb_pooled_attention_mma(void* out, const void* q, const void* k_t
     p.hq = hq; p.hkv = hkv; p.d = d; p.dv = dv; p.page_size = page_size; p.table_width = table_width; p.n_pages = n_pages;
     p.n_slots = n_slots; p.max_blocks = pool > 0 ? max_blocks : 0; p.window = window; p.pool = pool; p.ncv = pm_value_heads(hq, hkv);
     p.mode = 1; p.scale = scale;
+    p.ncv_mix = pm_value_heads(hq, hkv, pm_mix_heads(hq));
+    p.kept = kept;                                          // sized by kb_pooled_attention_mma_kept_floats for the same `longest`
+    p.kept_steps = kept != nullptr ? pm_kept_steps(form / 4, window, pool, p.max_blocks, longest) : 0;
+    KB_REQUIRE(kept == nullptr || longest > 0, "pooled_attention_mma: kept scores without the longest request's positions");
     cudaStream_t s = (cudaStream_t)stream;
     switch (form) {
         case 32 * 4 + 2: return pm_by_heads<32, 2>(p, tiles, s);

@@ -285,6 +285,10 @@ class StepBatch:
         tiles = self.memo[key]
         return tiles[:3] if tiles is not None else None
 
+    def longest_count(self) -> int:
+        """The most positions any row of this step has seen (its own included)."""
+        return int(self.plan.row_count.max()) if self.plan.rows else 0
+
     def longest_portion(self) -> int:
         """The most rows any request brings in this step (what sizes a launch of a block a run of a request's rows)."""
         return int(self.plan.q_len.max()) if len(self.plan.q_len) else 0

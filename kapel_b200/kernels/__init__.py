@@ -62,7 +62,7 @@ def library():
                 lib.kb_last_error.restype = ctypes.c_char_p
                 for name in ("kb_gemm_bf16_scratch_floats", "kb_paged_attention_scratch_floats", "kb_attention_mma_scratch_floats", "kb_sample_scratch_floats",
                              "kb_mlstm_state_floats", "kb_delta_state_floats", "kb_delta_scratch_floats", "kb_pooled_attention_scratch_floats",
-                             "kb_pooled_attention_mma_scratch_floats"):
+                             "kb_pooled_attention_mma_scratch_floats", "kb_pooled_attention_mma_kept_floats"):
                     getattr(lib, name).restype = ctypes.c_longlong
                 lib.kb_launch_count.restype = ctypes.c_ulonglong
                 lib.kb_set_pdl(1 if PDL else 0)
@@ -1151,6 +1151,9 @@ def pooled_attention_chunk() -> int:
     return _POOLED_CHUNK
 
 
+POOLED_KEPT_BYTES = int(_os.environ.get("KAPEL_B200_POOLED_KEPT_BYTES", str(4 << 30)))
+
+
 def pooled_attention_tile_rows() -> int:
     """Tokens a tile of the tensor-core kernel of `pooled_attention`."""
     return int(library().kb_pooled_attention_mma_tile_rows())
@@ -1163,7 +1166,7 @@ def pooled_attention_tiled(hq: int, hkv: int, d: int, dv: int) -> bool:
 
 def pooled_attention(q, k_table, v_table, pooled: Optional[torch.Tensor], block_table, row_entry, row_count, slots, talk, temp,
                      page_size: int, window: Optional[int], pool: int, scale: float, splits: int = 1, split_keys: int = 0,
-                     tiles=None) -> torch.Tensor:
+                     tiles=None, longest: Optional[int] = None) -> torch.Tensor:
     """Attention of each query row [rows, hq, d] over the last `window` tokens of its sequence (all with
     `window` None) and the pooled blocks of `pool` positions that lie wholly below the window (their mean
     keys and values in `pooled` [slots, blocks, hkv, d + dv], float32), in one softmax; score = q.k * scale
@@ -1171,7 +1174,8 @@ def pooled_attention(q, k_table, v_table, pooled: Optional[torch.Tensor], block_
     values. With `splits` > 1 the keys are cut into that many slices of `split_keys` across blocks.
     With `tiles` ((tile_entry, tile_row0, tile_nq) on the device: each request's rows in runs of at most
     `pooled_attention_tile_rows()`) bfloat16 rows of sizes that `pooled_attention_tiled` names go to the
-    tensor-core kernel, which walks a tile's keys for all heads together."""
+    tensor-core kernel, which walks a tile's keys for all heads together; `longest` is the most positions any row
+    has seen (read back from `row_count` if not given)."""
     rows, hq, d = q.shape
     _need(q, "pooled attention q")
     _need(k_table, "pooled attention k table", q.dtype)
@@ -1202,11 +1206,16 @@ def pooled_attention(q, k_table, v_table, pooled: Optional[torch.Tensor], block_
         for name, t in (("tile_entry", tile_entry), ("tile_row0", tile_row0), ("tile_nq", tile_nq)):
             _need(t, f"pooled attention {name}", torch.int32, (n_tiles,))
         scratch = _fresh((lib.kb_pooled_attention_mma_scratch_floats(rows, hq),), torch.float32, q.device)
+        # The first launch keeps its scores for the second where that costs at most POOLED_KEPT_BYTES of scratch memory.
+        if longest is None:
+            longest = int(row_count.max())
+        n_kept = int(lib.kb_pooled_attention_mma_kept_floats(n_tiles, hq, int(hkv), d, int(dv), int(window or 0), int(pool or 0), max_blocks, int(longest)))
+        kept = _fresh((n_kept,), torch.float32, q.device) if 0 < n_kept * 4 <= POOLED_KEPT_BYTES else None
         _check(lib.kb_pooled_attention_mma(
             _ptr(out), _ptr(q), _ptr(k_table), _ptr(v_table), _ptr(pooled if pool else None), ctypes.c_longlong(stride), n_slots, max_blocks,
             _ptr(block_table), _ptr(row_count), _ptr(tile_entry), _ptr(tile_row0), _ptr(tile_nq), n_tiles, _ptr(slots), _ptr(talk), _ptr(temp),
             rows, hq, int(hkv), d, int(dv), int(page_size), int(block_table.shape[1]), int(n_pages), int(window or 0), int(pool or 0), _f(scale),
-            _ptr(scratch), _stream()))
+            _ptr(scratch), _ptr(kept), int(longest), _stream()))
         return out
     need = lib.kb_pooled_attention_scratch_floats(rows, hq, int(dv), int(splits), int(split_keys))
     scratch = _fresh((need,), torch.float32, q.device) if need else None

@@ -157,7 +157,8 @@ class Attention(Part):
         splits, split_keys = batch.pooled_slices(s.window, s.pool) if hasattr(batch, "pooled_slices") else (1, 0)
         tiles = batch.pooled_tiles() if hasattr(batch, "pooled_tiles") else None
         y = K.pooled_attention(q, k_table, v_table, pooled, group.block_table, batch.row_entry, batch.row_count, batch.slots,
-                               self.talk, self.temp, self.ctx.page_size, s.window, s.pool, s.scale, splits, split_keys, tiles)
+                               self.talk, self.temp, self.ctx.page_size, s.window, s.pool, s.scale, splits, split_keys, tiles,
+                               batch.longest_count() if tiles is not None else None)
         width = product_width(self.ctx, s.num_heads * dv)
         y = y.view(y.shape[0], s.num_heads * dv)
         if width != y.shape[1]:

@@ -285,7 +285,7 @@ class PagedRequests:
 
 @pytest.mark.parametrize("dtype,tol", [(torch.float32, 1e-5), (torch.bfloat16, 1.5e-2)])
 @pytest.mark.parametrize("hq,hkv,d,dv,size,pool", [(4, 2, 16, 8, 20, 4), (6, 2, 16, 24, 13, 5), (1, 1, 32, 40, 1, 1), (3, 3, 10, 6, 7, 16), (8, 1, 64, 64, 64, 8),
-                                                    (5, 5, 24, 12, 33, 3), (2, 1, 96, 48, 96, 8), (16, 4, 8, 130, 30, 2)])
+                                                    (5, 5, 24, 12, 33, 3), (2, 1, 80, 32, 72, 6), (16, 4, 8, 130, 30, 2)])
 def test_window_and_pooled_blocks_in_one_softmax_with_mixed_heads(hq, hkv, d, dv, size, pool, dtype, tol):
     """Two sequences of unequal length in one launch: every query sees its window's tokens and the means of
     the blocks wholly below it, read from 32-bit means that a kernel took from the cache; scores carry the
@@ -322,12 +322,12 @@ def test_window_and_pooled_blocks_in_one_softmax_with_mixed_heads(hq, hkv, d, dv
     assert rel_err(got.float().cpu().numpy(), want) < tol
 
 
-@pytest.mark.parametrize("hq,hkv,d,dv,size,pool", [(8, 1, 64, 64, 64, 8), (2, 1, 96, 48, 96, 8), (16, 4, 32, 32, 40, 4), (12, 4, 16, 16, 9, 3),
+@pytest.mark.parametrize("hq,hkv,d,dv,size,pool", [(8, 1, 64, 64, 64, 8), (2, 1, 80, 32, 72, 6), (16, 4, 32, 32, 40, 4), (12, 4, 16, 16, 9, 3),
                                                     (32, 8, 16, 16, 20, 2), (8, 8, 32, 48, 24, 8), (3, 3, 16, 128, 7, 16), (16, 4, 128, 128, 50, 1),
                                                     (5, 1, 48, 80, 1, 1), (4, 2, 16, 16, 1000, 4)])
-def test_tiles_of_tokens_with_all_heads_on_tensor_cores(hq, hkv, d, dv, size, pool):
+def test_tiles_of_tokens_with_all_heads_on_tensor_cores(hq, hkv, d, dv, size, pool, monkeypatch):
     """The kernel for prompt portions: tiles of 16 tokens with all heads, two walks over the keys, the mix in
-    registers. One launch holds a portion that starts deep in a sequence (earlier rows lie in the cache only),
+    registers, from kept scores or from scores computed again. One launch holds a portion that starts deep in a sequence (earlier rows lie in the cache only),
     a whole short prompt, a single token, and a portion that starts one token before a tile would; also without
     a mix and without numbers of the heads."""
     from kapel_b200 import kernels as K
@@ -358,6 +358,12 @@ def test_tiles_of_tokens_with_all_heads_on_tensor_cores(hq, hkv, d, dv, size, po
                                   16, size, pool, scale)
         assert rel_err(got.float().cpu().numpy(), want) < 1.5e-2, mix
         assert rel_err(got.float().cpu().numpy(), rows.float().cpu().numpy()) < 1.5e-2, mix
+        # without room to keep the first walk's scores the second walk computes them again: the same weights
+        monkeypatch.setattr(K, "POOLED_KEPT_BYTES", 0)
+        again = K.pooled_attention(q, pr.kt, pr.vt, pr.means, pr.table, entry, count, pr.slots, dev(t_) if mix else None, dev(m_) if mix else None,
+                                   16, size, pool, scale, tiles=tiles, longest=max(lengths))
+        monkeypatch.undo()
+        assert rel_err(again.float().cpu().numpy(), got.float().cpu().numpy()) < 4e-3, mix
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
