@@ -324,7 +324,8 @@ def test_window_and_pooled_blocks_in_one_softmax_with_mixed_heads(hq, hkv, d, dv
 
 @pytest.mark.parametrize("hq,hkv,d,dv,size,pool", [(8, 1, 64, 64, 64, 8), (2, 1, 80, 32, 72, 6), (16, 4, 32, 32, 40, 4), (12, 4, 16, 16, 9, 3),
                                                     (32, 8, 16, 16, 20, 2), (8, 8, 32, 48, 24, 8), (3, 3, 16, 128, 7, 16), (16, 4, 128, 128, 50, 1),
-                                                    (5, 1, 48, 80, 1, 1), (4, 2, 16, 16, 1000, 4)])
+                                                    (5, 1, 48, 80, 1, 1), (4, 2, 16, 16, 1000, 4), (24, 8, 16, 112, 21, 5), (9, 3, 32, 16, 12, 4),
+                                                    (8, 2, 256, 64, 30, 7), (20, 20, 16, 32, 17, 2)])
 def test_tiles_of_tokens_with_all_heads_on_tensor_cores(hq, hkv, d, dv, size, pool, monkeypatch):
     """The kernel for prompt portions: tiles of 16 tokens with all heads, two walks over the keys, the mix in
     registers, from kept scores or from scores computed again. One launch holds a portion that starts deep in a sequence (earlier rows lie in the cache only),
