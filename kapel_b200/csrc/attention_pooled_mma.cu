@@ -531,8 +531,11 @@ pooled_mix_kernel(const PooledMmaParams p) {
         if (j0 + NK < n_keys) issue(j0 + NK, buf ^ 1);
         const float* bS = sc + (size_t)buf * hq * PM_ROWS * LDC;
         const bf16* bV = sV + (size_t)buf * p.ncv_mix * NK * ldv;
-        for (int e = tid; e < PM_ROWS * NK; e += PM_THREADS) {
+        // a (token, key) pair a thread, or two threads that share its output heads when a step has fewer pairs than threads
+        constexpr int EPT = PM_THREADS / (PM_ROWS * NK) > 0 ? PM_THREADS / (PM_ROWS * NK) : 1;
+        for (int e = tid % (PM_ROWS * NK); e < PM_ROWS * NK; e += PM_THREADS) {
             const int i = e / NK, jj = e - i * NK;
+            const int part = tid / (PM_ROWS * NK);
             float pg[HMAX];
 #pragma unroll
             for (int g = 0; g < HMAX; ++g) {
@@ -542,7 +545,7 @@ pooled_mix_kernel(const PooledMmaParams p) {
                     pg[g] = v == -INFINITY ? 0.f : __expf(v - s_m[g * PM_ROWS + i]) * s_il[g * PM_ROWS + i];
                 }
             }
-            for (int hl = 0; hl < nh; ++hl) {
+            for (int hl = part; hl < nh; hl += EPT) {
                 const float4* tr = reinterpret_cast<const float4*>(s_talk + hl * HMAX);
                 float w = 0.f;
 #pragma unroll
