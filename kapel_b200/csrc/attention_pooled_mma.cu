@@ -45,8 +45,8 @@ struct PooledMmaParams {
     const float* temp;         // [hq] or null
     bf16* out;                 // [rows, hq, dv]
     float* stats;              // [rows, hq, 2]
-    float* kept;               // [tiles, kept_steps, hq, 16, keys a step] the first launch's scores (-inf: not seen), or null
-    int kept_steps;            // steps a tile has room for
+    float* kept;               // [tiles, kept_steps, hq, 16, 16] the first launch's scores in runs of 16 keys (-inf: not seen), or null
+    int kept_steps;            // runs of 16 keys a tile has room for (an even number)
     long long slot_stride;
     int hq, hkv, d, dv, page_size, table_width, n_pages, n_slots, max_blocks;
     int window, pool;
@@ -259,7 +259,6 @@ pooled_mma_kernel(const PooledMmaParams p) {
         const bf16* bV = sV + (size_t)buf * p.ncv * NK * ldv;
         // ---- scores: an item is a head and 16 keys
         constexpr int NSUB = NK / 16;
-        float* keep = (p.mode == 1 && p.kept != nullptr) ? p.kept + ((size_t)t * p.kept_steps + j0 / NK) * hq * PM_ROWS * NK : nullptr;
         for (int item = warp; item < hq * NSUB; item += PM_WARPS) {
             const int g = item / NSUB, sub = item - g * NSUB;
             const int c = g / group;
@@ -300,12 +299,6 @@ pooled_mma_kernel(const PooledMmaParams p) {
                     }
                     sa[nt * 8 + e] = va;
                     sb[nt * 8 + e] = vb;
-                    if (e == 1 && keep != nullptr) {         // the pair (e = 0, 1) of neighbouring keys in one store
-                        float* ka = keep + (size_t)(g * PM_ROWS + ia) * NK + sub * 16 + (lane & 3) * 2 + nt * 8;
-                        float* kb2 = keep + (size_t)(g * PM_ROWS + ib) * NK + sub * 16 + (lane & 3) * 2 + nt * 8;
-                        *reinterpret_cast<float2*>(ka) = make_float2(sa[nt * 8], va);
-                        *reinterpret_cast<float2*>(kb2) = make_float2(sb[nt * 8], vb);
-                    }
                 }
         }
         __syncthreads();
@@ -392,6 +385,197 @@ pooled_mma_kernel(const PooledMmaParams p) {
                 if (i < nq) *reinterpret_cast<uint32_t*>(p.out + ((size_t)(r0 + i) * hq + h) * dv + col) = pm_pack(o[n][0], o[n][1]);
                 if (i + 8 < nq) *reinterpret_cast<uint32_t*>(p.out + ((size_t)(r0 + i + 8) * hq + h) * dv + col) = pm_pack(o[n][2], o[n][3]);
             }
+        }
+    }
+}
+
+// The first launch when scores are kept: a block (tile, 8 heads) computes its heads' scores only (their queries, their
+// kv heads' keys), keeps each (token, head)'s running maximum and sum for the table, and writes the masked scores to
+// scratch memory in runs of 16 keys [tile, run, head, token, 16]. Heads are independent here: no block repeats another's work.
+struct PmStatsLayout { unsigned q, k, ss, m, l, temp, ints, total; };
+
+__host__ __device__ inline PmStatsLayout pm_stats_layout(int hq, int d, int ncv, int nk, int stages) {
+    PmStatsLayout L;
+    unsigned at = 0;
+    const int heads = hq < PM_HEADS ? hq : PM_HEADS;
+    L.q = pm_take(at, (size_t)PM_ROWS * (heads * d + PM_PAD) * 2);
+    L.k = pm_take(at, (size_t)stages * ncv * nk * (d + PM_PAD) * 2);
+    L.ss = pm_take(at, (size_t)heads * PM_ROWS * (nk + 1) * 4);
+    L.m = pm_take(at, (size_t)heads * PM_ROWS * 4);
+    L.l = pm_take(at, (size_t)heads * PM_ROWS * 4);
+    L.temp = pm_take(at, (size_t)heads * 4);
+    L.ints = pm_take(at, (size_t)3 * PM_ROWS * 4);
+    L.total = at;
+    return L;
+}
+
+template <int NK, int STAGES>
+__global__ void __launch_bounds__(PM_THREADS, 1)
+pooled_stats_kernel(const PooledMmaParams p) {
+    extern __shared__ __align__(16) unsigned char pm_smem[];
+    const int hq = p.hq, hkv = p.hkv, d = p.d, dv = p.dv, group = p.hq / p.hkv;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int t = gridDim.x - 1 - blockIdx.x;
+    const int entry = p.tile_entry[t], r0 = p.tile_row0[t], nq = min(p.tile_nq[t], PM_ROWS);
+    const int h0 = blockIdx.y * PM_HEADS;
+    const int nh = min(PM_HEADS, hq - h0);
+    const int c_lo = h0 / group;
+    const int ncv = (h0 + nh - 1) / group - c_lo + 1;
+    const PmStatsLayout L = pm_stats_layout(hq, d, p.ncv, NK, STAGES);
+    bf16* sQ = reinterpret_cast<bf16*>(pm_smem + L.q);
+    bf16* sK = reinterpret_cast<bf16*>(pm_smem + L.k);
+    float* ss = reinterpret_cast<float*>(pm_smem + L.ss);
+    float* s_m = reinterpret_cast<float*>(pm_smem + L.m);
+    float* s_l = reinterpret_cast<float*>(pm_smem + L.l);
+    float* s_temp = reinterpret_cast<float*>(pm_smem + L.temp);
+    int* s_cnt = reinterpret_cast<int*>(pm_smem + L.ints);
+    int* s_first = s_cnt + PM_ROWS;
+    int* s_nb = s_first + PM_ROWS;
+    const int ldq = min(hq, PM_HEADS) * d + PM_PAD, ldk = d + PM_PAD, lds = NK + 1;
+    const int wide = d + dv;
+    const uint4 zero4 = make_uint4(0u, 0u, 0u, 0u);
+
+    if (tid < PM_ROWS) {
+        int c = tid < nq ? p.row_count[r0 + tid] : 0;
+        c = max(c, 0);
+        const bool past = p.window > 0 && c > p.window;
+        s_cnt[tid] = c;
+        s_first[tid] = past ? c - p.window : 0;
+        s_nb[tid] = (past && p.pool > 0) ? min((c - p.window) / p.pool, p.max_blocks) : 0;
+    }
+    {
+        const int qch = nh * d / 8;
+        for (int idx = tid; idx < PM_ROWS * qch; idx += PM_THREADS) {
+            const int i = idx / qch, ch = idx - i * qch;
+            const uint4 v = i < nq ? *reinterpret_cast<const uint4*>(p.q + ((size_t)(r0 + i) * hq + h0) * d + ch * 8) : zero4;
+            *reinterpret_cast<uint4*>(sQ + (size_t)i * ldq + ch * 8) = v;
+        }
+    }
+    for (int i = tid; i < nh; i += PM_THREADS) s_temp[i] = (p.temp != nullptr ? p.temp[h0 + i] : 1.f) * p.scale;
+    for (int i = tid; i < nh * PM_ROWS; i += PM_THREADS) {
+        s_m[i] = -INFINITY;
+        s_l[i] = 0.f;
+    }
+    __syncthreads();
+    int nb_max = 0, first_min = 0x7fffffff, c_max = 0;
+    for (int i = 0; i < nq; ++i) {
+        nb_max = max(nb_max, s_nb[i]);
+        first_min = min(first_min, s_first[i]);
+        c_max = max(c_max, s_cnt[i]);
+    }
+    const int n_keys = c_max > 0 ? nb_max + (c_max - first_min) : 0;
+    const int slot = p.slots[entry];
+    const float* pooled = p.pooled + (size_t)((slot > 0 && slot < p.n_slots) ? slot : 0) * p.slot_stride;
+    const int* pages = p.block_table + (size_t)entry * p.table_width;
+    const int ia = lane >> 2, ib = ia + 8;
+    const int nb_a = s_nb[ia], lo_a = nb_max + s_first[ia] - first_min, hi_a = nb_max + s_cnt[ia] - first_min;
+    const int nb_b = s_nb[ib], lo_b = nb_max + s_first[ib] - first_min, hi_b = nb_max + s_cnt[ib] - first_min;
+    const int all_nb = s_nb[0], all_lo = nb_max + s_first[nq - 1] - first_min, all_hi = nb_max + s_cnt[0] - first_min;
+
+    constexpr int TPK = PM_THREADS / NK;
+    auto issue = [&](int j0, int buf) {
+        const int jj = tid / TPK, sub = tid - jj * TPK;
+        const int j = j0 + jj;
+        bf16* kd = sK + (size_t)buf * p.ncv * NK * ldk + (size_t)jj * ldk;
+        long long row = -1;
+        if (j >= nb_max && j < n_keys) {
+            const int pos = first_min + (j - nb_max);
+            const int lp = pos / p.page_size;
+            const int page = lp < p.table_width ? pages[lp] : -1;
+            if (page >= 0 && page < p.n_pages) row = (long long)page * hkv * p.page_size + (pos - lp * p.page_size);
+        }
+        if (row >= 0) {
+            for (int cl = 0; cl < ncv; ++cl) {
+                const bf16* src = p.k_table + (size_t)(row + (long long)(c_lo + cl) * p.page_size) * d;
+                for (int ch = sub; ch * 8 < d; ch += TPK) pm_cp_async16(kd + (size_t)cl * NK * ldk + ch * 8, src + ch * 8);
+            }
+        } else if (j < nb_max) {
+            for (int cl = 0; cl < ncv; ++cl) {
+                const float* src = pooled + ((size_t)j * hkv + c_lo + cl) * wide;
+                for (int ch = sub; ch * 8 < d; ch += TPK) {
+                    const float4 a = *reinterpret_cast<const float4*>(src + ch * 8), b = *reinterpret_cast<const float4*>(src + ch * 8 + 4);
+                    *reinterpret_cast<uint4*>(kd + (size_t)cl * NK * ldk + ch * 8) = make_uint4(pm_pack(a.x, a.y), pm_pack(a.z, a.w), pm_pack(b.x, b.y), pm_pack(b.z, b.w));
+                }
+            }
+        } else {
+            for (int cl = 0; cl < ncv; ++cl)
+                for (int ch = sub; ch * 8 < d; ch += TPK) *reinterpret_cast<uint4*>(kd + (size_t)cl * NK * ldk + ch * 8) = zero4;
+        }
+        pm_cp_async_commit();
+    };
+
+    if (STAGES == 2 && n_keys > 0) issue(0, 0);
+    for (int j0 = 0; j0 < n_keys; j0 += NK) {
+        const int buf = STAGES == 2 ? (j0 / NK) & 1 : 0;
+        if (STAGES == 1) issue(j0, 0);
+        pm_cp_async_wait_all();
+        __syncthreads();                                     // the step's keys are in; everyone has left the step before
+        if (STAGES == 2 && j0 + NK < n_keys) issue(j0 + NK, buf ^ 1);
+        const bf16* bK = sK + (size_t)buf * p.ncv * NK * ldk;
+        constexpr int NSUB = NK / 16;
+        for (int item = warp; item < nh * NSUB; item += PM_WARPS) {
+            const int gl = item / NSUB, sub = item - gl * NSUB;
+            const int g = h0 + gl;
+            const int cl = g / group - c_lo;
+            float acc[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+            const bf16* qa = sQ + (size_t)(lane & 15) * ldq + gl * d + (lane >> 4) * 8;
+            const bf16* kf = bK + ((size_t)cl * NK + sub * 16 + (lane & 7) + ((lane >> 4) << 3)) * ldk + ((lane >> 3) & 1) * 8;
+            for (int ks = 0; ks < d; ks += 16) {
+                uint32_t a[4], b[4];
+                pm_ldmatrix_x4(a, qa + ks);
+                pm_ldmatrix_x4(b, kf + ks);
+                pm_mma(acc[0], a, b[0], b[1]);
+                pm_mma(acc[1], a, b[2], b[3]);
+            }
+            const float tg = s_temp[gl];
+            const int js = j0 + sub * 16;
+            const bool whole = js + 16 <= all_nb || (js >= all_lo && js + 16 <= all_hi);
+            float* sa = ss + (size_t)(gl * PM_ROWS + ia) * lds + sub * 16 + (lane & 3) * 2;
+            float* sb = ss + (size_t)(gl * PM_ROWS + ib) * lds + sub * 16 + (lane & 3) * 2;
+            float* run = p.kept + ((size_t)t * p.kept_steps + js / 16) * hq * PM_ROWS * 16;
+            float* ka = run + (size_t)(g * PM_ROWS + ia) * 16 + (lane & 3) * 2;
+            float* kb2 = run + (size_t)(g * PM_ROWS + ib) * 16 + (lane & 3) * 2;
+#pragma unroll
+            for (int nt = 0; nt < 2; ++nt) {
+                float va[2], vb[2];
+#pragma unroll
+                for (int e = 0; e < 2; ++e) {
+                    const int j = js + nt * 8 + (lane & 3) * 2 + e;
+                    const bool seen_a = whole || j < nb_a || (j >= lo_a && j < hi_a);
+                    const bool seen_b = whole || j < nb_b || (j >= lo_b && j < hi_b);
+                    va[e] = seen_a ? acc[nt][e] * tg : -INFINITY;
+                    vb[e] = seen_b ? acc[nt][2 + e] * tg : -INFINITY;
+                    sa[nt * 8 + e] = va[e];
+                    sb[nt * 8 + e] = vb[e];
+                }
+                *reinterpret_cast<float2*>(ka + nt * 8) = make_float2(va[0], va[1]);
+                *reinterpret_cast<float2*>(kb2 + nt * 8) = make_float2(vb[0], vb[1]);
+            }
+        }
+        __syncthreads();
+        for (int pr = tid; pr < nh * PM_ROWS; pr += PM_THREADS) {
+            const float* row = ss + (size_t)pr * lds;
+            float mx = -INFINITY;
+#pragma unroll
+            for (int jj = 0; jj < NK; ++jj) mx = fmaxf(mx, row[jj]);
+            const float old = s_m[pr];
+            const float top = fmaxf(old, mx);
+            if (top != -INFINITY) {
+                float l = 0.f;
+#pragma unroll
+                for (int jj = 0; jj < NK; ++jj) l += __expf(row[jj] - top);
+                s_l[pr] = (old == -INFINITY ? 0.f : s_l[pr] * __expf(old - top)) + l;
+                s_m[pr] = top;
+            }
+        }
+        // (the next step's first barrier stands between these reads and its scores)
+    }
+    for (int pr = tid; pr < nh * PM_ROWS; pr += PM_THREADS) {
+        const int gl = pr / PM_ROWS, i = pr - gl * PM_ROWS;
+        if (i < nq) {
+            float* st = p.stats + ((size_t)(r0 + i) * hq + h0 + gl) * 2;
+            st[0] = s_m[pr];
+            st[1] = s_l[pr];
         }
     }
 }
@@ -487,11 +671,11 @@ pooled_mix_kernel(const PooledMmaParams p) {
     constexpr int TPK = PM_THREADS / NK;
     auto issue = [&](int j0, int buf) {
         // the step's scores: rows of NK floats, [hq * 16] of them
-        const float* from = p.kept + ((size_t)t * p.kept_steps + j0 / NK) * hq * PM_ROWS * NK;
+        const float* from = p.kept + ((size_t)t * p.kept_steps + j0 / 16) * hq * PM_ROWS * 16;
         float* to = sc + (size_t)buf * hq * PM_ROWS * LDC;
         for (int idx = tid; idx < hq * PM_ROWS * (NK / 4); idx += PM_THREADS) {
             const int row = idx / (NK / 4), ch = idx - row * (NK / 4);
-            pm_cp_async16(to + (size_t)row * LDC + ch * 4, from + (size_t)row * NK + ch * 4);
+            pm_cp_async16(to + (size_t)row * LDC + ch * 4, from + ((size_t)(ch >> 2) * hq * PM_ROWS + row) * 16 + (ch & 3) * 4);
         }
         const int jj = tid / TPK, sub = tid - jj * TPK;
         const int j = j0 + jj;
@@ -630,18 +814,6 @@ static int pm_launch(PooledMmaParams p, int tiles, cudaStream_t s) {
     pooled_mma_kernel<NK, HMAX, DVMAX, STAGES><<<dim3(tiles, 1), PM_THREADS, smem, s>>>(p);
     if (int e = check_launch("pooled_attention_mma statistics")) return e;
     p.mode = 2;
-    if (p.kept != nullptr) {
-        if (pm_mix_heads(p.hq) == 16) {
-            const unsigned mix_smem = pm_mix_layout(p.hq, p.dv, p.ncv_mix, NK, 16).total;
-            if (mix_smem > 48 * 1024) cudaFuncSetAttribute(pooled_mix_kernel<NK, HMAX, DVMAX, 16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)mix_smem);
-            pooled_mix_kernel<NK, HMAX, DVMAX, 16><<<dim3(tiles, (p.hq + 15) / 16), PM_THREADS, mix_smem, s>>>(p);
-        } else {
-            const unsigned mix_smem = pm_mix_layout(p.hq, p.dv, p.ncv_mix, NK, 8).total;
-            if (mix_smem > 48 * 1024) cudaFuncSetAttribute(pooled_mix_kernel<NK, HMAX, DVMAX, 8>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)mix_smem);
-            pooled_mix_kernel<NK, HMAX, DVMAX, 8><<<dim3(tiles, 1), PM_THREADS, mix_smem, s>>>(p);
-        }
-        return check_launch("pooled_attention_mma mix");
-    }
     pooled_mma_kernel<NK, HMAX, DVMAX, STAGES><<<dim3(tiles, (p.hq + PM_HEADS - 1) / PM_HEADS), PM_THREADS, smem, s>>>(p);
     return check_launch("pooled_attention_mma");
 }
@@ -658,6 +830,57 @@ static int pm_by_heads(const PooledMmaParams& p, int tiles, cudaStream_t s) {
     return pm_by_values<NK, 32, STAGES>(p, tiles, s);
 }
 
+// ---- with kept scores: the statistics launch by blocks of heads, then the mix launch
+static int pm_mix_keys(int hq, int hkv, int dv) {           // keys a step of the mix launch: 32, 16 or 0 (does not fit)
+    const int hb = pm_mix_heads(hq), ncv = pm_value_heads(hq, hkv, hb);
+    if (pm_mix_layout(hq, dv, ncv, 32, hb).total <= PM_SMEM_LIMIT) return 32;
+    if (pm_mix_layout(hq, dv, ncv, 16, hb).total <= PM_SMEM_LIMIT) return 16;
+    return 0;
+}
+
+static int pm_stats_form(int hq, int hkv, int d) {          // keys a step * 4 + stages of the statistics launch, or 0
+    const int ncv = pm_value_heads(hq, hkv);
+    const int forms[4][2] = {{32, 2}, {16, 2}, {32, 1}, {16, 1}};
+    for (const auto& f : forms)
+        if (pm_stats_layout(hq, d, ncv, f[0], f[1]).total <= PM_SMEM_LIMIT) return f[0] * 4 + f[1];
+    return 0;
+}
+
+template <int NK, int STAGES>
+static int pm_launch_stats(const PooledMmaParams& p, int tiles, cudaStream_t s) {
+    const unsigned smem = pm_stats_layout(p.hq, p.d, p.ncv, NK, STAGES).total;
+    if (smem > 48 * 1024) cudaFuncSetAttribute(pooled_stats_kernel<NK, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    pooled_stats_kernel<NK, STAGES><<<dim3(tiles, (p.hq + PM_HEADS - 1) / PM_HEADS), PM_THREADS, smem, s>>>(p);
+    return check_launch("pooled_attention_mma statistics");
+}
+
+template <int NK, int HMAX, int DVMAX, int HB>
+static int pm_launch_mix(const PooledMmaParams& p, int tiles, cudaStream_t s) {
+    const unsigned smem = pm_mix_layout(p.hq, p.dv, p.ncv_mix, NK, HB).total;
+    if (smem > 48 * 1024) cudaFuncSetAttribute(pooled_mix_kernel<NK, HMAX, DVMAX, HB>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    pooled_mix_kernel<NK, HMAX, DVMAX, HB><<<dim3(tiles, (p.hq + HB - 1) / HB), PM_THREADS, smem, s>>>(p);
+    return check_launch("pooled_attention_mma mix");
+}
+
+template <int NK>
+static int pm_mix_by_sizes(const PooledMmaParams& p, int tiles, cudaStream_t s) {
+    if (p.hq <= 8) return p.dv <= 64 ? pm_launch_mix<NK, 8, 64, 8>(p, tiles, s) : pm_launch_mix<NK, 8, 128, 8>(p, tiles, s);
+    if (p.hq <= 16) return p.dv <= 64 ? pm_launch_mix<NK, 16, 64, 16>(p, tiles, s) : pm_launch_mix<NK, 16, 128, 16>(p, tiles, s);
+    return p.dv <= 64 ? pm_launch_mix<NK, 32, 64, 16>(p, tiles, s) : pm_launch_mix<NK, 32, 128, 16>(p, tiles, s);
+}
+
+static int pm_run_kept(const PooledMmaParams& p, int tiles, cudaStream_t s) {
+    int e;
+    switch (pm_stats_form(p.hq, p.hkv, p.d)) {
+        case 32 * 4 + 2: e = pm_launch_stats<32, 2>(p, tiles, s); break;
+        case 16 * 4 + 2: e = pm_launch_stats<16, 2>(p, tiles, s); break;
+        case 32 * 4 + 1: e = pm_launch_stats<32, 1>(p, tiles, s); break;
+        default: e = pm_launch_stats<16, 1>(p, tiles, s); break;
+    }
+    if (e) return e;
+    return pm_mix_keys(p.hq, p.hkv, p.dv) == 32 ? pm_mix_by_sizes<32>(p, tiles, s) : pm_mix_by_sizes<16>(p, tiles, s);
+}
+
 }  // namespace kb
 
 using namespace kb;
@@ -671,11 +894,11 @@ extern "C" long long kb_pooled_attention_mma_scratch_floats(int rows, int hq) { 
 
 // Steps a tile needs room for when the first launch keeps its scores for the second: the most keys a tile of a
 // request that has seen `longest` positions reads, over the keys a step.
-static int pm_kept_steps(int nk, int window, int pool, int max_blocks, int longest) {
+static int pm_kept_steps(int window, int pool, int max_blocks, int longest) {      // runs of 16 keys, an even number
     long long tokens = window > 0 ? (longest < window + PM_ROWS - 1 ? longest : window + PM_ROWS - 1) : longest;
     long long blocks = (window > 0 && pool > 0 && longest > window) ? (longest - window) / pool : 0;
     if (blocks > max_blocks) blocks = max_blocks;
-    return (int)((tokens + blocks + nk - 1) / nk);
+    return (int)((tokens + blocks + 31) / 32) * 2;
 }
 
 // Floats of scratch memory for the kept scores (0: these sizes are not taken).
@@ -683,9 +906,8 @@ extern "C" long long kb_pooled_attention_mma_kept_floats(int tiles, int hq, int 
                                                          int longest) {
     const int form = pm_form(hq, hkv, d, dv);
     if (form <= 0 || tiles <= 0 || longest <= 0) return 0;
-    const int nk = form / 4;
-    if (pm_mix_layout(hq, dv, pm_value_heads(hq, hkv, pm_mix_heads(hq)), nk, pm_mix_heads(hq)).total > PM_SMEM_LIMIT) return 0;
-    return (long long)tiles * pm_kept_steps(nk, window, pool, pool > 0 ? max_blocks : 0, longest) * hq * PM_ROWS * nk;
+    if (pm_mix_keys(hq, hkv, dv) == 0 || pm_stats_form(hq, hkv, d) == 0) return 0;
+    return (long long)tiles * pm_kept_steps(window, pool, pool > 0 ? max_blocks : 0, longest) * hq * PM_ROWS * 16;
 }
 
 extern "C" int kb_pooled_attention_mma(void* out, const void* q, const void* k_table, const void* v_table, const float* pooled,
@@ -712,9 +934,10 @@ extern "C" int kb_pooled_attention_mma(void* out, const void* q, const void* k_t
     p.mode = 1; p.scale = scale;
     p.ncv_mix = pm_value_heads(hq, hkv, pm_mix_heads(hq));
     p.kept = kept;                                          // sized by kb_pooled_attention_mma_kept_floats for the same `longest`
-    p.kept_steps = kept != nullptr ? pm_kept_steps(form / 4, window, pool, p.max_blocks, longest) : 0;
+    p.kept_steps = kept != nullptr ? pm_kept_steps(window, pool, p.max_blocks, longest) : 0;
     KB_REQUIRE(kept == nullptr || longest > 0, "pooled_attention_mma: kept scores without the longest request's positions");
     cudaStream_t s = (cudaStream_t)stream;
+    if (kept != nullptr) return pm_run_kept(p, tiles, s);
     switch (form) {
         case 32 * 4 + 2: return pm_by_heads<32, 2>(p, tiles, s);
         case 16 * 4 + 2: return pm_by_heads<16, 2>(p, tiles, s);
