@@ -10,10 +10,11 @@
 //           maximum and sum; a thread holds all heads' weights of its (token, key) pairs in registers,
 //           mixes them for the block's output heads and leaves them in shared memory as bfloat16;
 //           each warp multiplies one output head's mixed weights with its kv head's values.
-// Where scratch memory allows, the first launch also keeps its (masked) scores, and the second launch is
-// `pooled_mix_kernel` instead: a block (tile, 8 or 16 output heads) fetches a step's scores of all heads by
-// cp.async, with the values of its heads' kv heads, and normalises, mixes and multiplies: no queries, no
-// keys, no score computed twice.
+// Where scratch memory allows, the scores are kept between the launches instead: `pooled_stats_kernel` (a
+// block a tile and 8 heads: only their queries and their kv heads' keys) leaves the statistics and the masked
+// scores, and `pooled_mix_kernel` (a block a tile and 8 or 16 output heads) fetches a step's scores of all
+// heads by cp.async, with the values of its heads' kv heads, and normalises, mixes and multiplies: no
+// queries, no keys, no score computed twice. `pooled_mma_kernel`'s two modes are what runs otherwise.
 // Keys and values of a step lie in shared memory for all kv heads (the pooled means, 32-bit in their
 // table, are rounded to bfloat16 on the way in); fragments come by ldmatrix. Which keys a token sees:
 // the blocks b < floor((c - window) / pool) and the tokens [max(0, c - window), c), c the positions it
