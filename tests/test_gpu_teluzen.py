@@ -609,6 +609,24 @@ def test_recorded_passes_give_what_eager_ones_give(models):
         assert rel_err(outs[1][step], outs[0][step]) < 2e-6, f"step {step}"
 
 
+def test_portions_on_tensor_cores_through_recorded_passes(models):
+    """Three requests fed in the same portions of 128, 128 and 144 tokens, in bfloat16 at sizes the tiled kernel takes:
+    the second and third meet recorded passes of the first one's shapes (scratch memory for the kept scores
+    included); every request against the plain forward pass at the portions' edges, tile edges and last rows."""
+    raw = models["D"][1]
+    eng = engine_for(models, "D", "bfloat16", graphs=True)
+    tb = TraceBuilder()
+    want = {}
+    for k in ("x", "y", "z"):
+        tokens = random_tokens(np.random.default_rng(ord(k)), 400, raw["vocab"])
+        want[k] = plain(models, "D", tokens)
+        tb.step([(k, tokens[:128], [0, 15, 16, 63, 127])])
+        tb.step([(k, tokens[128:256], [0, 1, 100, 127])])
+        tb.step([(k, tokens[256:], [0, 7, 8, 143])], end=[k])
+    check_rows(run_trace_engine(eng, tb.steps), tb, want, "bfloat16", "recorded portions")
+    assert eng.recorded_passes > 0
+
+
 ODD = {"architecture": "Teluzen", "vocab": 77, "width": 52, "max_positions": 300, "norm": {"eps": 1e-6}, "layers": [
     layer(3, 1, 12, 10, 0.3, 9, 7, {"base": 80.0, "dims": 6, "scaling": SCALED}, True, {"kind": "dense", "ff": 13}),
     layer(5, 1, 6, 10, 0.5, 11, 2, {"base": 7.0, "dims": 6}, True, moe(11, 3, 2, 5))]}
