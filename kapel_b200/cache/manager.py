@@ -55,10 +55,30 @@ class StateSpec:
 
 @dataclass(frozen=True)
 class CacheNeeds:
-    """What one layer's mixer keeps between steps; both may be None."""
+    """What one layer keeps between steps; all may be absent. `state` is the layer's one state table;
+    `states` holds further tables by name, for a layer made of several parts that each keep something
+    (a block's own state beside its mixer's, two mixers side by side): `named(prefix)` moves a part's
+    needs under a name, `merged(other)` puts two parts' needs together."""
 
     paged: Optional[PagedKV] = None
     state: Optional[StateSpec] = None
+    states: Tuple[Tuple[str, StateSpec], ...] = ()
+
+    def named(self, prefix: str) -> "CacheNeeds":
+        """The same needs with every state table under `prefix` (the unnamed one becomes `prefix` itself)."""
+        out = [(prefix, self.state)] if self.state is not None else []
+        out += [(f"{prefix}.{name}", spec) for name, spec in self.states]
+        return CacheNeeds(paged=self.paged, state=None, states=tuple(out))
+
+    def merged(self, other: "CacheNeeds") -> "CacheNeeds":
+        if self.paged is not None and other.paged is not None:
+            raise ValueError("two parts of one layer both ask for pages; a layer has one paged cache")
+        if self.state is not None and other.state is not None:
+            raise ValueError("two parts of one layer both ask for the layer's unnamed state")
+        names = [n for n, _ in self.states] + [n for n, _ in other.states]
+        if len(set(names)) != len(names):
+            raise ValueError(f"two parts of one layer ask for a state of the same name: {sorted(names)}")
+        return CacheNeeds(paged=self.paged or other.paged, state=self.state or other.state, states=self.states + other.states)
 
 
 @dataclass
@@ -154,8 +174,12 @@ class CacheManager:
             g = self._by_needs[n.paged]
             self.groups[g].layers.append(layer)
             self.group_of_layer[layer] = g
-        self.state_specs: Dict[int, StateSpec] = {l: n.state for l, n in needs.items() if n.state is not None}
-        self.states: Dict[int, object] = {}
+        # a layer's unnamed state is keyed by the layer, a named one by (layer, name)
+        self.state_specs: Dict[object, StateSpec] = {l: n.state for l, n in needs.items() if n.state is not None}
+        for l, n in needs.items():
+            for name, spec in getattr(n, "states", ()):
+                self.state_specs[(l, name)] = spec
+        self.states: Dict[object, object] = {}
         self._sequences: Dict[Hashable, int] = {}                # sequence -> its slot (1 ..; 0 is the padding rows')
         self._lib = host_library()
         n_groups = len(self.groups)

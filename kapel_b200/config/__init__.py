@@ -2,6 +2,7 @@
 from .fusitar import FusitarConfig
 from .gemma2 import ConfigError, Gemma2Config
 from .kofutar import KofutarConfig
+from .lokedra import LokedraConfig
 from .teluzen import TeluzenConfig
 from .registry import (
     architectures,
@@ -18,8 +19,11 @@ from .spec import (
     BlockSpec,
     DeltaSpec,
     EmbedSpec,
+    ForgetGateSpec,
     GatedMLPSpec,
+    GeneralDeltaSpec,
     HeadSpec,
+    InputAddSpec,
     InputMixSpec,
     LatentAttentionSpec,
     MLPSpec,
@@ -27,6 +31,7 @@ from .spec import (
     ModelSpec,
     MoESpec,
     NormSpec,
+    ParallelMixerSpec,
     PositionSpec,
     RopeScaling,
     ScheduleEntry,

@@ -15,6 +15,7 @@ from typing import Dict, Tuple
 from .fusitar import FusitarConfig
 from .gemma2 import ConfigError, Gemma2Config
 from .kofutar import KofutarConfig
+from .lokedra import LokedraConfig
 from .teluzen import TeluzenConfig
 
 _ARCHITECTURES: Dict[str, type] = {}
@@ -102,3 +103,4 @@ register_architecture(Gemma2Config, Gemma2Config.architecture, Gemma2Config.mode
 register_architecture(FusitarConfig, FusitarConfig.architecture, FusitarConfig.model_type)
 register_architecture(KofutarConfig, KofutarConfig.architecture, KofutarConfig.model_type)
 register_architecture(TeluzenConfig, TeluzenConfig.architecture, TeluzenConfig.model_type)
+register_architecture(LokedraConfig, LokedraConfig.architecture, LokedraConfig.model_type)

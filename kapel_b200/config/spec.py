@@ -77,6 +77,15 @@ class AttentionSpec:
     rows, before they are cached) are kept for later layers; "mix": v <- (1 - l) v + l v_source with l
     the one value of role vmix, and the mixed v is what is cached; the layers of one `value_mix_key`
     share a source.
+
+    `conv` t > 0: every channel of the query and of the key projection goes through a causal convolution
+    over the last t rows (roles q_conv, k_conv: [channels, t], the last weight for the row itself; zeros
+    before a request's first row; no activation), directly after the projection and its bias; the last
+    t - 1 projected rows are state of a request. `values_are_keys`: there is no v; a key as it is cached is
+    also the value. `block_mask` B > 0: a query at position i sees a key j <= i only if floor(i / B) =
+    floor(j / B), blocks counted from position 0. `unit_sink`: 1 joins the softmax's denominator (a key
+    of score 0 without a value). `out_bias`: o has a bias (role o_bias); with `qk_bias` q and k have
+    biases and v has none.
     """
 
     hidden: int
@@ -103,6 +112,12 @@ class AttentionSpec:
     talk: bool = False
     value_mix: Optional[str] = None
     value_mix_key: str = "values"
+    conv: int = 0
+    values_are_keys: bool = False
+    block_mask: int = 0
+    unit_sink: bool = False
+    qk_bias: bool = False
+    out_bias: bool = False
 
 
 @dataclass(frozen=True)
@@ -160,6 +175,62 @@ class DeltaSpec:
 
 
 @dataclass(frozen=True)
+class GeneralDeltaSpec:
+    """The generalized delta rule: a matrix memory S [head_dim, head_dim] a head and request with a
+    decay a key channel and the removal of what lies along the unit key.
+
+    r, k, v [heads, head_dim] from the input. Per head and key channel the decay
+    w = exp(-`decay_scale` sigmoid(w2 tanh(w1 h) + w0)) and the removal rate a = sigmoid(a h + a_bias).
+    With u = k / sqrt(sum k^2 + `unit_eps`): S <- diag(w) S - (a u)(u^T S) + k v^T (both first terms
+    read the old S); o = S^T r. Each head's o is divided by its root mean square (`eps`), times the
+    weight `norm` [heads head_dim], times sigmoid(g h), then o. `weights`: r, k, v, g, a, a_bias, w1,
+    w2, w0, norm, o; the small net's hidden width is w1's number of rows (`lora`).
+    """
+
+    hidden: int
+    num_heads: int
+    head_dim: int
+    lora: int
+    eps: float
+    weights: Mapping[str, str]
+    decay_scale: float = 0.6065306597126334          # e^(-1/2)
+    unit_eps: float = 1e-6
+    kind: str = "general_delta"
+
+
+@dataclass(frozen=True)
+class ForgetGateSpec:
+    """Linear attention whose forget gate also decides what is written (HGRN2): a matrix memory
+    S [head_dim, v_head_dim] a head and request.
+
+    q = silu(q h) [heads, head_dim], v = v h [heads, v_head_dim], f = l + (1 - l) sigmoid(f h + f_bias)
+    per head and channel with the lower bound l (role lower, [heads head_dim]). S <- diag(f) S +
+    (1 - f) v^T; o = S^T q. Each head's o is RMS-normed over v_head_dim (`eps`) with the weight `norm`
+    [v_head_dim] shared by the heads, then o. `weights`: q, f, f_bias, lower, v, norm, o.
+    """
+
+    hidden: int
+    num_heads: int
+    head_dim: int
+    v_head_dim: int
+    eps: float
+    weights: Mapping[str, str]
+    kind: str = "forget_gate"
+
+
+@dataclass(frozen=True)
+class ParallelMixerSpec:
+    """Two mixers side by side that read the same input: `left_scale` left(h) + `right_scale` right(h).
+    Each keeps its own pages and state; at most one of them may ask for pages."""
+
+    left: object
+    right: object
+    left_scale: float
+    right_scale: float
+    kind: str = "parallel"
+
+
+@dataclass(frozen=True)
 class MLSTMSpec:
     """A matrix memory with exponential gates (xLSTM's mLSTM), one state a head and request.
 
@@ -194,7 +265,8 @@ class MoESpec:
     groups of neighbours, a group scores the sum of its `group_top` best choice scores, and only
     experts of the best `keep_groups` groups can be chosen; `renormalize` divides the chosen
     weights by their sum. `weights`: router, correction (or absent), and the patterns `up` and
-    `down` with `{e}` for the expert's number.
+    `down` with `{e}` for the expert's number. The gated activation "clamped_swish" with `limit` L and
+    `swish_alpha` a: g = min(gate h, L), u = clamp(up h, -L, L), the unit is g sigmoid(a g) (u + 1).
     """
 
     hidden: int
@@ -210,6 +282,8 @@ class MoESpec:
     renormalize: bool = False
     gated: bool = False
     shared: Optional[object] = None
+    limit: Optional[float] = None
+    swish_alpha: float = 1.702
     kind: str = "moe"
 
 
@@ -243,13 +317,19 @@ class BlockSpec:
     branches (`ffn` None: a layer of its mixer alone, with the first two norms);
     kind "prenorm": `pre_mixer` and `pre_ffn` only; kind "postnorm": the branches read
     the residual itself and only their outputs are normed (`post_mixer`, `post_ffn`), and `ffn`
-    may be None for a layer without a feed-forward.
+    may be None for a layer without a feed-forward. kind "parallel": one norm `pre`, and both branches
+    read its output h: x <- x + (mixer(h) + ffn(h)); with `scales` = (name, name) each branch is first
+    multiplied, channel by channel, by a weight [hidden] (the second is absent without a feed-forward);
+    with `shift` (a tensor [hidden]) the mixer, and only the mixer, reads h_t + (h_(t-1) - h_t) * shift,
+    h_(t-1) the row before (zeros for a request's first row), which is state of a request.
     """
 
     mixer: object
     ffn: object
     norms: Mapping[str, NormSpec]
     kind: str = "sandwich"
+    scales: Optional[Tuple[str, Optional[str]]] = None
+    shift: Optional[str] = None
 
 
 @dataclass(frozen=True)
@@ -277,6 +357,14 @@ class InputMixSpec:
     hidden: int
     weight: str
     kind: str = "input_mix"
+
+
+@dataclass(frozen=True)
+class InputAddSpec:
+    """x <- x + x0: the embedding's output x0 is added to the stream."""
+
+    hidden: int
+    kind: str = "input_add"
 
 
 @dataclass(frozen=True)

@@ -309,7 +309,7 @@ extern "C" int kb_latent_attention_mma(void* out, const void* q, const void* tab
     p.q = q; p.k_table = table; p.v_table = table; p.block_table = block_table; p.row_entry = nullptr; p.row_count = row_count;
     p.out = out; p.partial = slots > 1 ? scratch : nullptr; p.rows = rows; p.hq = hq; p.hkv = 1; p.d = d; p.page_size = page_size;
     p.table_width = table_width; p.n_pages = n_pages; p.dv = dv; p.v_stride = d; p.sinks = sinks; p.vec = 1; p.window = 0; p.keep = 0;
-    p.keep_slots = 0; p.slots = slots; p.chunk = chunk; p.scale = scale; p.cap = 0.f;
+    p.keep_slots = 0; p.block = 0; p.slots = slots; p.chunk = chunk; p.scale = scale; p.cap = 0.f;
     const int heads_per_tile = hq < LM_ROWS ? hq : LM_ROWS;
     const int head_slices = (hq + heads_per_tile - 1) / heads_per_tile;
     const int tokens_per_tile = LM_ROWS / heads_per_tile;

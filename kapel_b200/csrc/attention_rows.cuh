@@ -2,7 +2,8 @@
 // Attention over the paged cache, one query row at a time ("rows" kernels), for any element
 // type. A query row that has seen c positions (its own included) reads keys
 // [max(0, c - window), c) of its sequence through the block table, and with `keep` > 0 also the
-// keys [0, keep) that lie below its window; score = scale * q.k, then
+// keys [0, keep) that lie below its window; with `block` > 0 only the keys of its own block of that
+// many positions (blocks are counted from position 0); score = scale * q.k, then
 // cap * tanh(score / cap) if a cap is given, softmax over what it sees, weighted sum of values;
 // a row that sees nothing gives zeros. Scores, soft cap, softmax and sums are 32-bit.
 //
@@ -66,6 +67,7 @@ struct AttParams {
     const float* sinks;       // [hq] or null: a term e^sink in the denominator of every row of the head
     int vec;                  // 1: a key is a whole number of 16-byte pieces and is loaded as such
     int window;               // 0: none
+    int block;                // > 0: a row at position i sees only the keys from floor(i / block) * block on (blocks counted from position 0)
     int keep;                 // with a window: the keys [0, keep) stay visible below it
     int keep_slots;           // ceil(keep / CHUNK) with a window and keep > 0, else 0: the slots of those keys
     int slots;                // chunk slots a row may touch, the kept keys' included
@@ -77,7 +79,8 @@ struct AttParams {
 // first `keep_slots` slots are chunks of the kept first keys below the window's start, the others
 // the window's chunks, counted from the chunk that holds its first key.
 __device__ __forceinline__ void slot_range(const AttParams& p, int count, int z, int& lo, int& hi) {
-    const int first = (p.window > 0 && count > p.window) ? count - p.window : 0;
+    int first = (p.window > 0 && count > p.window) ? count - p.window : 0;
+    if (p.block > 0 && count > 0) first = max(first, (count - 1) / p.block * p.block);
     if (z < p.keep_slots) {
         lo = z * p.chunk;
         hi = min(min(p.keep, first), (z + 1) * p.chunk);

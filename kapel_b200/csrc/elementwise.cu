@@ -306,6 +306,19 @@ __global__ void glu_bf16x8_kernel(__nv_bfloat16* __restrict__ out, const __nv_bf
     *reinterpret_cast<uint4*>(out + r * n + i) = make_uint4(o4[0], o4[1], o4[2], o4[3]);
 }
 
+// out[r, i] = g' sigmoid(alpha g') (u' + 1) with g' = min(x[r, i], limit) and u' = clamp(x[r, n + i], -limit, limit):
+// the gated unit with both halves bounded and the linear half shifted by one.
+template <typename TI, typename T>
+__global__ void glu_clamped_kernel(T* __restrict__ out, const Src<TI> x, long long rows, int n, float limit, float alpha) {
+    const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= rows * n) return;
+    const long long r = idx / n;
+    const int i = (int)(idx % n);
+    const float g = fminf(x.at(r * 2 * n + i), limit);
+    const float u = fminf(fmaxf(x.at(r * 2 * n + n + i), -limit), limit);
+    Elem<T>::store(out + idx, g / (1.f + expf(-alpha * g)) * (u + 1.f));
+}
+
 template <typename TO, typename TI>
 __global__ void cast_kernel(TO* __restrict__ out, const TI* __restrict__ in, long long n) {
     const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
@@ -568,4 +581,22 @@ extern "C" int kb_gather_rows_f32(float* out, const float* x, const int* rows, i
     if (n == 0) return 0;
     gather_rows_f32_kernel<<<n, 256, 0, (cudaStream_t)stream>>>(out, x, rows, n, width, src_rows);
     return check_launch("gather_rows");
+}
+
+extern "C" int kb_glu_clamped(void* out, int out_dt, const void* x, int in_dt, int splits, long long split_stride,
+                              long long rows, int n, float limit, float alpha, void* stream) {
+    KB_REQUIRE(rows >= 0 && n > 0, "glu_clamped: rows %lld, width %d", rows, n);
+    KB_REQUIRE(limit > 0.f, "glu_clamped: a bound of %g", limit);
+    KB_REQUIRE(splits >= 1, "glu_clamped: %d slices", splits);
+    if (rows == 0) return 0;
+    const unsigned blocks = (unsigned)((rows * n + 255) / 256);
+    cudaStream_t s = (cudaStream_t)stream;
+#define KB_GLUC(TI, T) \
+    glu_clamped_kernel<TI, T><<<blocks, 256, 0, s>>>((T*)out, Src<TI>{(const TI*)x, splits, (size_t)split_stride}, rows, n, limit, alpha)
+    if (in_dt == KB_DT_F32 && out_dt == KB_DT_F32) KB_GLUC(float, float);
+    else if (in_dt == KB_DT_F32 && out_dt == KB_DT_BF16) KB_GLUC(float, bf16);
+    else if (in_dt == KB_DT_BF16 && out_dt == KB_DT_BF16) KB_GLUC(bf16, bf16);
+    else return fail("glu_clamped: dtype codes %d -> %d are not known", in_dt, out_dt);
+#undef KB_GLUC
+    return check_launch("glu_clamped");
 }

@@ -101,8 +101,10 @@ __global__ void head_gate_kernel(TO* __restrict__ out, const TY* __restrict__ y,
     for (int c = lane; c < e; c += 32) {
         float v = Elem<TY>::load(yp + c) * inv;
         if (w != nullptr) v *= Elem<TW>::load(w + (size_t)h * e + c);
-        const float z = gate.at((size_t)r * row_width + g_off + (size_t)h * e + c);
-        v *= act == 1 ? z / (1.f + expf(-z)) : 1.f / (1.f + expf(-z));       // silu(z) or sigmoid(z)
+        if (act != 2) {                                                          // 2: no gate
+            const float z = gate.at((size_t)r * row_width + g_off + (size_t)h * e + c);
+            v *= act == 1 ? z / (1.f + expf(-z)) : 1.f / (1.f + expf(-z));       // silu(z) or sigmoid(z)
+        }
         Elem<TO>::store(out + (size_t)r * out_stride + (size_t)h * e + c, v);
     }
     // a row wider than its heads (padding for the product that follows) ends in zeros
@@ -513,7 +515,7 @@ extern "C" int kb_head_gate(void* out, int out_dt, const void* y, int y_dt, cons
                             long long split_stride, int row_width, int g_off, const void* w, int w_dt, int unit, float eps,
                             long long rows, int heads, int e, int out_stride, int act, void* stream) {
     KB_REQUIRE(rows >= 0 && heads > 0 && e > 0, "head_gate: rows %lld, heads %d of %d", rows, heads, e);
-    KB_REQUIRE(act == 0 || act == 1, "head_gate: gate activation code %d is not known (0 sigmoid, 1 silu)", act);
+    KB_REQUIRE(act >= 0 && act <= 2, "head_gate: gate activation code %d is not known (0 sigmoid, 1 silu, 2 none)", act);
     KB_REQUIRE(out_stride >= heads * e, "head_gate: output rows of %d values for %d heads of %d", out_stride, heads, e);
     KB_REQUIRE(row_width > 0 && g_off >= 0 && g_off + heads * e <= row_width, "head_gate: gate columns %d.. do not fit a row of %d", g_off, row_width);
     KB_REQUIRE(splits >= 1 && (splits == 1 || split_stride >= rows * row_width), "head_gate: %d slices %lld apart", splits, split_stride);

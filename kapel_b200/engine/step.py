@@ -71,6 +71,12 @@ class Engine:
                  graphs: bool = True, strict: bool = False):
         self.device = device or require_device()
         self.dtype = parse_dtype(dtype)
+        if hasattr(config, "with_shapes"):
+            # sizes that only the tensors give (a configuration that has them already stays as it is)
+            if hasattr(tensors, "shape") and callable(tensors.shape):
+                config = config.with_shapes(tensors.shape)
+            elif isinstance(tensors, dict):
+                config = config.with_shapes(lambda name: tensors[name].shape)
         self.config = config
         self.raw_config = raw_config
         self.spec = config.to_spec()

@@ -62,7 +62,7 @@ def library():
                 lib.kb_last_error.restype = ctypes.c_char_p
                 for name in ("kb_gemm_bf16_scratch_floats", "kb_paged_attention_scratch_floats", "kb_attention_mma_scratch_floats", "kb_sample_scratch_floats",
                              "kb_mlstm_state_floats", "kb_delta_state_floats", "kb_delta_scratch_floats", "kb_pooled_attention_scratch_floats",
-                             "kb_pooled_attention_mma_scratch_floats", "kb_pooled_attention_mma_kept_floats"):
+                             "kb_pooled_attention_mma_scratch_floats", "kb_pooled_attention_mma_kept_floats", "kb_decay_scan_scratch_floats"):
                     getattr(lib, name).restype = ctypes.c_longlong
                 lib.kb_launch_count.restype = ctypes.c_ulonglong
                 lib.kb_set_pdl(1 if PDL else 0)
@@ -354,6 +354,19 @@ def glu(x, activation: str, out_dtype: Optional[torch.dtype] = None) -> torch.Te
     return out
 
 
+def glu_clamped(x, limit: float, alpha: float, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+    """g' sigmoid(alpha g') (u' + 1) for a stacked gate|up product (a tensor or a SplitSum), with
+    g' = min(gate, limit) and u' = clamp(up, -limit, limit)."""
+    src, in_dt, splits, stride = _src(x, "glu_clamped input")
+    rows, two_n = x.shape
+    n = two_n // 2
+    out_dtype = out_dtype or (src.dtype if not isinstance(x, SplitSum) else torch.bfloat16)
+    out = _fresh((rows, n), out_dtype, src.device)
+    _check(library().kb_glu_clamped(_ptr(out), _dt(out, "glu_clamped output"), _ptr(src), in_dt, splits, ctypes.c_longlong(stride),
+                                    ctypes.c_longlong(rows), n, _f(limit), _f(alpha), _stream()))
+    return out
+
+
 def cast(x: torch.Tensor, dtype: torch.dtype) -> torch.Tensor:
     _need(x, "cast input")
     out = _fresh(x.shape, dtype, x.device)
@@ -568,8 +581,9 @@ def attention_chunk() -> int:
 
 def paged_attention_rows(q, k_table, v_table, block_table, row_entry, row_count, page_size: int, window: Optional[int],
                          scale: float, softcap: Optional[float], slots: int, keep_first: int = 0,
-                         sinks: Optional[torch.Tensor] = None, value_dim: Optional[int] = None) -> torch.Tensor:
-    """Attention of each query row over its sequence's pages; `slots` is the largest number of
+                         sinks: Optional[torch.Tensor] = None, value_dim: Optional[int] = None, block: int = 0) -> torch.Tensor:
+    """Attention of each query row over its sequence's pages; with `block` > 0 a row at position i sees
+    only the keys from floor(i / block) * block on (`slots` as for a window of `block` positions); `slots` is the largest number of
     key chunks (of `attention_chunk()` positions, cut at absolute multiples) any row touches, plus,
     with a window and `keep_first` > 0, the chunks of the first `keep_first` keys, which stay
     visible below the window (`attention_keep_slots`). The values' size is the v table's last, or
@@ -595,10 +609,10 @@ def paged_attention_rows(q, k_table, v_table, block_table, row_entry, row_count,
     need = lib.kb_paged_attention_scratch_floats(rows, hq, dv, int(slots))
     scratch = _fresh((need,), torch.float32, q.device) if need else None
     _check(
-        lib.kb_paged_attention_rows(_ptr(out), _ptr(q), _ptr(k_table), _ptr(v_table), _dt(q, "attention q"), _ptr(block_table),
+        lib.kb_paged_attention_rows_blocked(_ptr(out), _ptr(q), _ptr(k_table), _ptr(v_table), _dt(q, "attention q"), _ptr(block_table),
                                     _ptr(row_entry), _ptr(row_count), rows, hq, hkv, d, int(dv), int(page_size), int(block_table.shape[1]),
                                     int(n_pages), int(window or 0), int(keep_first or 0), int(slots), _f(scale), _f(softcap or 0.0),
-                                    _ptr(scratch), int(v_stride), _ptr(sinks), _stream())
+                                    _ptr(scratch), int(v_stride), _ptr(sinks), int(block or 0), _stream())
     )
     return out
 
@@ -798,7 +812,7 @@ def paged_attention_mma(q, k_table, v_table, block_table, row_count, tiles, page
 
 # ------------------------------------------------------------------------------------------
 # Mixers whose roles share one stacked product: a role is a run of columns of each row.
-GATE_ACTS = {"sigmoid": 0, "silu": 1}
+GATE_ACTS = {"sigmoid": 0, "silu": 1, "none": 2}        # "none": the gate is not read
 
 
 def _stacked(x, what: str):
@@ -1014,6 +1028,153 @@ def delta_scan(stacked, q_off: int, k_off: int, v_off: int, b_off: int, a_off: i
         int(b_off), int(a_off), _ptr(conv), _ptr(a_log), _ptr(dt_bias), _ptr(state), int(state.shape[0]), ctypes.c_longlong(per),
         _ptr(row_entry), _ptr(start), _ptr(end), _ptr(slots), int(entries), rows, heads, kv_heads, d, e, int(taps), _f(q_scale),
         _f(unit_eps), _stream()))
+    return out
+
+
+def _ranges(ranges, slots, entries: int, what: str):
+    start, end = ranges
+    _need(start, f"{what} entry starts", torch.int32)
+    _need(end, f"{what} entry ends", torch.int32)
+    _need(slots, f"{what} slots", torch.int32)
+    if min(start.numel(), end.numel(), slots.numel()) < entries:
+        raise KernelError(f"{what}: {entries} requests but ranges or slots for fewer")
+    return start, end
+
+
+def token_shift(h: torch.Tensor, mu: torch.Tensor, state: torch.Tensor, row_entry, ranges, slots, entries: int, keep: bool = True,
+                pad_to: int = 0) -> torch.Tensor:
+    """y[r] = h[r] + (h[r-1] - h[r]) * mu, channel by channel, for h [rows, width]; the row before a
+    request's first row of the step is its slot's line of `state` [slots, width] (float32), and with
+    `keep` that line then becomes the request's last h of the step. The result's rows may be wider
+    (`pad_to`, zeros behind)."""
+    _need(h, "token_shift input")
+    rows, width = h.shape
+    _need(mu, "token_shift weights", torch.float32, (width,))
+    _need(state, "token_shift state", torch.float32)
+    if state.dim() != 2 or state.shape[1] != width:
+        raise KernelError(f"token_shift: a state table of {tuple(state.shape)}, expected [slots, {width}]")
+    _need(row_entry, "token_shift row_entry", torch.int32, (rows,))
+    start, end = _ranges(ranges, slots, entries, "token_shift")
+    out_width = max(int(pad_to), width)
+    out = _fresh((rows, out_width), h.dtype, h.device)
+    _check(library().kb_token_shift(_ptr(out), _ptr(h), _dt(h, "token_shift input"), _ptr(mu), _ptr(state), _ptr(row_entry), _ptr(start),
+                                    _ptr(end), _ptr(slots), int(entries), int(state.shape[0]), rows, width, out_width, int(bool(keep)),
+                                    _stream()))
+    return out
+
+
+def conv_state_floats(hq: int, hkv: int, d: int, taps: int) -> int:
+    """Floats a request keeps between steps for the short convolutions on queries and keys: the last
+    taps - 1 inputs of every channel."""
+    return (taps - 1) * (hq + hkv) * d
+
+
+def conv_append(stacked, q_off: int, k_off: int, bias: Optional[torch.Tensor], conv: torch.Tensor, state: torch.Tensor, row_entry,
+                ranges, slots, entries: int, lines, k_table, hq: int, hkv: int, d: int, taps: int, write_kv: bool,
+                out_dtype: torch.dtype, pad_to: int = 0) -> torch.Tensor:
+    """Queries [rows, hq d] (or `pad_to` wide, zeros behind) and keys through a short causal convolution
+    over time, one filter a channel (`conv` [(hq + hkv) d, taps] float32, the last weight for the row
+    itself), after `bias` [(hq + hkv) d]; the keys are written at each row's line of `k_table`
+    [pages, hkv, page_size, d]. `state` [slots, (taps - 1) (hq + hkv) d] holds every request's last inputs."""
+    src, dt, splits, stride, rows, width = _stacked(stacked, "conv_append input")
+    channels = (hq + hkv) * d
+    _need(conv, "conv_append filters", torch.float32, (channels, taps))
+    if bias is not None:
+        _need(bias, "conv_append bias", torch.float32, (channels,))
+    _need(state, "conv_append state", torch.float32)
+    if state.dim() != 2 or state.shape[1] != conv_state_floats(hq, hkv, d, taps):
+        raise KernelError(f"conv_append: a state table of {tuple(state.shape)}, expected [slots, {conv_state_floats(hq, hkv, d, taps)}]")
+    _need(row_entry, "conv_append row_entry", torch.int32, (rows,))
+    start, end = _ranges(ranges, slots, entries, "conv_append")
+    q_width = max(int(pad_to), hq * d)
+    q = _fresh((rows, q_width), out_dtype, src.device)
+    table_lines, page_size = 0, 0
+    if write_kv:
+        _need(lines, "conv_append lines", torch.int32, (rows,))
+        _need(k_table, "conv_append table", out_dtype)
+        if k_table.dim() != 4 or k_table.shape[1] != hkv or k_table.shape[3] != d:
+            raise KernelError(f"conv_append: a table of {tuple(k_table.shape)} is not [pages, {hkv}, page_size, {d}]")
+        table_lines = k_table.shape[0] * k_table.shape[2]
+        page_size = k_table.shape[2]
+    _check(library().kb_conv_append(
+        _ptr(q), q_width, _ptr(k_table if write_kv else None), _CODES[out_dtype], _ptr(src), dt, splits, ctypes.c_longlong(stride), width,
+        int(q_off), int(k_off), _ptr(bias), _ptr(conv), _ptr(state), int(state.shape[0]), _ptr(row_entry), _ptr(start), _ptr(end),
+        _ptr(slots), _ptr(lines if write_kv else None), int(entries), rows, int(hq), int(hkv), int(d), int(taps), int(bool(write_kv)),
+        ctypes.c_longlong(table_lines), int(page_size), _stream()))
+    return q
+
+
+def gdelta_scan(stacked, r_off: int, k_off: int, v_off: int, a_off: int, w1_off: int, w2: torch.Tensor, w0: torch.Tensor,
+                a_bias: torch.Tensor, decay_scale: float, unit_eps: float, state: torch.Tensor, ranges, slots, entries: int,
+                heads: int, d: int) -> torch.Tensor:
+    """The generalized delta rule's read-out [rows, heads, d] (float32, not yet normed) over the rows of a
+    step, request by request in row order, from and into `state` [slots, heads, d, d]. Per head, with the
+    decay w = exp(-decay_scale sigmoid(w2 tanh(w1 h) + w0)), the removal rate a = sigmoid(a h + a_bias) and
+    the unit key u = k / sqrt(sum k^2 + unit_eps): S <- diag(w) S - (a u)(u^T S) + k v^T, o = S^T r. The
+    columns r_off, k_off, v_off, a_off (heads d each) and w1_off (the small net's hidden layer, before
+    its tanh) of `stacked` hold the projections."""
+    src, dt, splits, stride, rows, width = _stacked(stacked, "gdelta input")
+    n = heads * d
+    _need(w2, "gdelta decay weights", torch.float32)
+    if w2.dim() != 2 or w2.shape[0] != n:
+        raise KernelError(f"gdelta: decay weights of {tuple(w2.shape)}, expected [{n}, hidden]")
+    lora = int(w2.shape[1])
+    _need(w0, "gdelta decay bias", torch.float32, (n,))
+    _need(a_bias, "gdelta removal bias", torch.float32, (n,))
+    _need(state, "gdelta state", torch.float32)
+    if state.dim() != 2 or state.shape[1] != n * d:
+        raise KernelError(f"gdelta: a state table of {tuple(state.shape)}, expected [slots, {n * d}]")
+    start, end = _ranges(ranges, slots, entries, "gdelta")
+    lib = library()
+    out = _fresh((rows, heads, d), torch.float32, src.device)
+    scratch = _fresh((max(1, int(lib.kb_decay_scan_scratch_floats(rows, heads, d, d, 1))),), torch.float32, src.device)
+    _check(lib.kb_gdelta_scan(
+        _ptr(out), _ptr(scratch), _ptr(src), dt, splits, ctypes.c_longlong(stride), width, int(r_off), int(k_off), int(v_off), int(a_off),
+        int(w1_off), lora, _ptr(w2), _ptr(w0), _ptr(a_bias), _f(decay_scale), _f(unit_eps), _ptr(state), int(state.shape[0]),
+        _ptr(start), _ptr(end), _ptr(slots), int(entries), rows, int(heads), int(d), _stream()))
+    return out
+
+
+def gate_scan(stacked, q_off: int, f_off: int, v_off: int, f_bias: torch.Tensor, lower: torch.Tensor, state: torch.Tensor, ranges,
+              slots, entries: int, heads: int, d: int, e: int) -> torch.Tensor:
+    """The read-out [rows, heads, e] (float32, not yet normed) of a matrix memory behind a forget gate that
+    also decides what is written: q = silu(.), f = lower + (1 - lower) sigmoid(. + f_bias) per head and
+    channel; S <- diag(f) S + (1 - f) v^T, o = S^T q; `state` [slots, heads e d]."""
+    src, dt, splits, stride, rows, width = _stacked(stacked, "gate_scan input")
+    _need(f_bias, "gate_scan gate bias", torch.float32, (heads * d,))
+    _need(lower, "gate_scan lower bounds", torch.float32, (heads * d,))
+    _need(state, "gate_scan state", torch.float32)
+    if state.dim() != 2 or state.shape[1] != heads * d * e:
+        raise KernelError(f"gate_scan: a state table of {tuple(state.shape)}, expected [slots, {heads * d * e}]")
+    start, end = _ranges(ranges, slots, entries, "gate_scan")
+    lib = library()
+    out = _fresh((rows, heads, e), torch.float32, src.device)
+    scratch = _fresh((max(1, int(lib.kb_decay_scan_scratch_floats(rows, heads, d, e, 0))),), torch.float32, src.device)
+    _check(lib.kb_gate_scan(
+        _ptr(out), _ptr(scratch), _ptr(src), dt, splits, ctypes.c_longlong(stride), width, int(q_off), int(f_off), int(v_off),
+        _ptr(f_bias), _ptr(lower), _ptr(state), int(state.shape[0]), _ptr(start), _ptr(end), _ptr(slots), int(entries), rows,
+        int(heads), int(d), int(e), _stream()))
+    return out
+
+
+def weighted_sum2(a, va: torch.Tensor, b=None, vb: Optional[torch.Tensor] = None, vc: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """a * va + b * vb + vc in float32 for branches [rows, width] (tensors or SplitSums) with a weight a
+    channel each (float32 [width]); `b` and `vc` may be absent."""
+    a_src, a_dt, a_splits, a_stride = _src(a, "weighted_sum2 first branch")
+    rows, width = a.shape
+    _need(va, "weighted_sum2 first weights", torch.float32, (width,))
+    b_src, b_dt, b_splits, b_stride = None, F32, 1, 0
+    if b is not None:
+        if tuple(b.shape) != (rows, width):
+            raise KernelError(f"weighted_sum2: branches of {tuple(a.shape)} and {tuple(b.shape)}")
+        b_src, b_dt, b_splits, b_stride = _src(b, "weighted_sum2 second branch")
+        _need(vb, "weighted_sum2 second weights", torch.float32, (width,))
+    if vc is not None:
+        _need(vc, "weighted_sum2 offsets", torch.float32, (width,))
+    out = _fresh((rows, width), torch.float32, a_src.device)
+    _check(library().kb_weighted_sum2(_ptr(out), _ptr(a_src), a_dt, a_splits, ctypes.c_longlong(a_stride), _ptr(va), _ptr(b_src), b_dt,
+                                      b_splits, ctypes.c_longlong(b_stride), _ptr(vb if b is not None else None), _ptr(vc),
+                                      ctypes.c_longlong(rows), int(width), _stream()))
     return out
 
 
@@ -1350,7 +1511,8 @@ _TIMED = ("embed", "rope_table", "rope_append", "glu", "cast", "gather_rows", "r
           "paged_attention_rows", "paged_attention_mma", "sample", "proj_norm_append", "head_gate", "mlstm_scan", "moe_route",
           "moe_sort", "moe_grouped", "moe_combine", "gemm_glu_fused", "paged_attention_decode_fused", "layernorm", "concat2",
           "head_norm_rope_append", "latent_append", "head_linear", "delta_scan", "latent_attention_mma", "proj_rope_append",
-          "pool_blocks", "pooled_attention", "act")
+          "pool_blocks", "pooled_attention", "act", "token_shift", "conv_append", "gdelta_scan", "gate_scan", "weighted_sum2",
+          "glu_clamped")
 _timing = None
 _originals = {}
 

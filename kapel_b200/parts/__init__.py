@@ -2,15 +2,18 @@
 from .attention import Attention
 from .base import (BuildContext, LayerCache, Part, linear, matrix_for, matrix_named, pad_columns, product_width,
                    require_product_widths, stack_rows)
-from .block import PostNormBlock, PreNormBlock, SandwichBlock
+from .block import ParallelBlock, PostNormBlock, PreNormBlock, SandwichBlock
 from .delta import Delta
 from .embedding import Embedding, VocabHead
 from .feed_forward import MLP, GatedMLP
-from .input_mix import InputMix
+from .forget_gate import ForgetGate
+from .general_delta import GeneralDelta
+from .input_mix import InputAdd, InputMix
 from .latent_attention import LatentAttention
 from .mlstm import MLSTM
 from .moe import MoE
 from .norm import LayerNorm, RMSNorm, add_branch
+from .parallel import ParallelMixer
 from .position import NoPosition, Rope
 from .registry import (
     build_part,
@@ -28,7 +31,11 @@ register_part("mixer", "attention", Attention)
 register_part("mixer", "mlstm", MLSTM)
 register_part("mixer", "latent_attention", LatentAttention)
 register_part("mixer", "delta", Delta)
+register_part("mixer", "general_delta", GeneralDelta)
+register_part("mixer", "forget_gate", ForgetGate)
+register_part("mixer", "parallel", ParallelMixer)
 register_part("merge", "input_mix", InputMix)
+register_part("merge", "input_add", InputAdd)
 register_part("feed_forward", "gated_mlp", GatedMLP)
 register_part("feed_forward", "mlp", MLP)
 register_part("feed_forward", "moe", MoE)
@@ -39,6 +46,7 @@ register_part("position", "none", NoPosition)
 register_part("block", "sandwich", SandwichBlock)
 register_part("block", "prenorm", PreNormBlock)
 register_part("block", "postnorm", PostNormBlock)
+register_part("block", "parallel", ParallelBlock)
 register_part("embedding", "embedding", Embedding)
 register_part("head", "vocab_head", VocabHead)
 

@@ -22,6 +22,12 @@ weights or values mixed with another layer's runs the fourth path (`forward_pool
 product in 32-bit; one kernel for biases, the norms over the whole projections, the rotation (either
 pairing), the value mix and the append; one that leaves the means of every block the step completes
 in the request's slot of the layer's state table; then the attention kernel over window and blocks.
+
+A spec with short convolutions on queries and keys whose values are its keys runs the fifth path
+(`forward_convolved`): the stacked product q|k in 32-bit; one kernel that adds the biases, convolves every
+channel over the last rows (the rows before the step from the request's state) and appends the keys, which
+are also the values (one table); the row-wise attention kernel with the block mask and 1 in the
+denominator; the output product, whose bias the caller may add (`forward_unbiased`, `out_bias`).
 """
 from __future__ import annotations
 
@@ -41,6 +47,15 @@ class Attention(Part):
         dv = spec.v_head_dim or spec.head_dim
         qd, kvd = spec.num_heads * spec.head_dim, spec.num_kv_heads * spec.head_dim
         w = spec.weights
+        if spec.values_are_keys:
+            out = {w["q"]: (qd, spec.hidden), w["k"]: (kvd, spec.hidden), w["o"]: (spec.hidden, qd)}
+            if spec.conv:
+                out[w["q_conv"]], out[w["k_conv"]] = (qd, spec.conv), (kvd, spec.conv)
+            if spec.qk_bias:
+                out[w["q_bias"]], out[w["k_bias"]] = (qd,), (kvd,)
+            if spec.out_bias:
+                out[w["o_bias"]] = (spec.hidden,)
+            return out
         out = {w["q"]: (qd, spec.hidden), w["k"]: (kvd, spec.hidden), w["v"]: (spec.num_kv_heads * dv, spec.hidden),
                w["o"]: (spec.hidden, spec.num_heads * dv)}
         if spec.gated:
@@ -64,6 +79,18 @@ class Attention(Part):
             raise ValueError(f"attention: {spec.num_heads} heads over {spec.num_kv_heads} kv heads")
         self.v_dim = spec.v_head_dim or spec.head_dim
         self.by_head = bool(spec.q_head_norm or spec.k_head_norm)
+        self.convolved = bool(spec.conv or spec.values_are_keys or spec.block_mask or spec.unit_sink or spec.qk_bias or spec.out_bias)
+        self.out_bias = None
+        if self.convolved:
+            if not (spec.values_are_keys and 1 <= spec.conv <= 8):
+                raise ValueError("attention: a block mask, 1 in the denominator or biases on q, k and o are built for the path with "
+                                 f"convolutions (1 to 8 rows, got {spec.conv}) whose values are its keys")
+            if (self.by_head or spec.gated or spec.q_norm or spec.k_norm or spec.keep_first or spec.softcap or spec.window or spec.bias
+                    or spec.pool or spec.head_temp or spec.talk or spec.value_mix or spec.v_head_dim not in (None, spec.head_dim)):
+                raise ValueError("attention: convolutions together with norms, a gate, a window, a soft cap, pooled blocks, mixed heads or "
+                                 "values of their own are not built")
+            if spec.block_mask < 0:
+                raise ValueError(f"attention: blocks of {spec.block_mask} positions")
         self.pooled = bool(spec.bias or spec.pool or spec.head_temp or spec.talk or spec.value_mix)
         if self.pooled:
             if self.by_head or spec.gated or spec.keep_first or spec.softcap:
@@ -80,23 +107,38 @@ class Attention(Part):
         for n in (spec.q_head_norm, spec.k_head_norm):
             if n is not None and (n.kind != "rms" or n.width != spec.head_dim):
                 raise ValueError(f"attention: a norm over each head must be an RMS norm of width {spec.head_dim}")
-        if not self.general and not self.by_head and not self.pooled and spec.head_dim % 16:
+        if not self.general and not self.by_head and not self.pooled and not self.convolved and spec.head_dim % 16:
             raise ValueError(f"attention: head_dim {spec.head_dim} must be a multiple of 16 for the kernels")
         if spec.keep_first < 0 or (spec.keep_first and not spec.window):
             raise ValueError(f"attention: {spec.keep_first} first keys kept with window {spec.window}")
         for n, width in ((spec.q_norm, spec.num_heads * spec.head_dim), (spec.k_norm, spec.num_kv_heads * spec.head_dim)):
             if n is not None and (n.kind != "rms" or n.width != width):
                 raise ValueError(f"attention: a norm over the whole projection must be an RMS norm of width {width}")
-        if not self.general and not self.by_head and not self.pooled:
+        if not self.general and not self.by_head and not self.pooled and not self.convolved:
             require_product_widths(ctx, "attention", hidden_size=spec.hidden,
                                    **{"num_attention_heads x value size": spec.num_heads * self.v_dim})
         self.position = build_part("position", spec.position, ctx)
         if self.general and self.position.rotary_dim:
             raise ValueError("attention: a rotation together with projection norms, a gate, kept first keys or another value size is not built")
+        if self.convolved and self.position.rotary_dim:
+            raise ValueError("attention: a rotation together with convolutions is not built")
         if not self.pooled and getattr(self.position, "neighbours", False):
             raise ValueError("attention: the rotation of neighbouring components is built for the path with biases, pooled blocks or mixed heads only")
 
+    def load_convolved(self, tensors):
+        s, w, dev = self.spec, self.spec.weights, self.ctx.device
+        self.w_qkv = stack_rows(self.ctx, tensors, [w["q"], w["k"]], "attention")
+        self.w_o = pad_columns(self.ctx, matrix_named(self.ctx, tensors, w["o"]))
+        f32 = lambda n: tensors[n].to(dev).float().contiguous()
+        self.conv = torch.cat([f32(w["q_conv"]), f32(w["k_conv"])], dim=0).contiguous()
+        self.qk_bias = torch.cat([f32(w["q_bias"]), f32(w["k_bias"])]).contiguous() if s.qk_bias else None
+        self.out_bias = f32(w["o_bias"]) if s.out_bias else None
+        self.ones = torch.ones((s.hidden,), dtype=torch.float32, device=dev) if s.out_bias else None
+        self.sinks = torch.zeros((s.num_heads,), dtype=torch.float32, device=dev) if s.unit_sink else None      # e^0 = 1 in the denominator
+
     def load(self, tensors):
+        if self.convolved:
+            return self.load_convolved(tensors)
         w = self.spec.weights
         names = [w["q"], w["k"], w["v"]] + ([w["g"]] if self.spec.gated else [])
         self.w_qkv = stack_rows(self.ctx, tensors, names, "attention")
@@ -121,6 +163,10 @@ class Attention(Part):
 
     def cache_needs(self) -> CacheNeeds:
         s = self.spec
+        if self.convolved:
+            # one table: a key is also the value. A block mask gives no pages back (a block's pages stay until the request ends).
+            states = (("conv", StateSpec((K.conv_state_floats(s.num_heads, s.num_kv_heads, s.head_dim, s.conv),))),)
+            return CacheNeeds(paged=PagedKV(s.num_kv_heads, s.head_dim, None, 0, None, shared_values=True), states=states)
         if self.pooled and s.pool:
             # The pages keep the window's tokens, and a block's tokens until its last one has come (the
             # means are taken from the pages then); the means of a request's blocks are its state.
@@ -162,6 +208,27 @@ class Attention(Part):
         width = product_width(self.ctx, s.num_heads * dv)
         y = y.view(y.shape[0], s.num_heads * dv)
         if width != y.shape[1]:
+            y = K.pad_cols(y, width)
+        return linear(self.ctx, y, self.w_o, keep_split=True)
+
+    def forward_unbiased(self, h, batch, cache):
+        """`forward` without the output product's bias (`out_bias`), for a caller that adds it in a kernel of its own."""
+        if not self.convolved:
+            return self.forward(h, batch, cache)
+        s = self.spec
+        nq = s.num_heads * s.head_dim
+        stacked = linear(self.ctx, h, self.w_qkv, out_dtype=torch.float32, keep_split=True)
+        k_table, _ = cache.tables()
+        group = batch.groups[cache.group]
+        q = K.conv_append(stacked, 0, nq, self.qk_bias, self.conv, cache.state_of("conv"), batch.row_entry, batch.entry_ranges(),
+                          batch.slots, batch.entries, group.lines, k_table, s.num_heads, s.num_kv_heads, s.head_dim, s.conv, cache.owns,
+                          self.ctx.dtype)
+        y = K.paged_attention_rows(q.view(-1, s.num_heads, s.head_dim), k_table, k_table, group.block_table, batch.row_entry,
+                                   batch.row_count, self.ctx.page_size, None, s.scale, None, batch.attention_slots(s.block_mask or None),
+                                   sinks=self.sinks, block=s.block_mask)
+        y = y.view(y.shape[0], nq)
+        width = product_width(self.ctx, nq)
+        if width != nq:
             y = K.pad_cols(y, width)
         return linear(self.ctx, y, self.w_o, keep_split=True)
 
@@ -225,6 +292,9 @@ class Attention(Part):
 
     def forward(self, h, batch, cache):
         s = self.spec
+        if self.convolved:
+            y = self.forward_unbiased(h, batch, cache)
+            return K.weighted_sum2(y, self.ones, None, None, self.out_bias) if self.out_bias is not None else y
         if self.pooled:
             return self.forward_pooled(h, batch, cache)
         if self.by_head:

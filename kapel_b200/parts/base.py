@@ -66,10 +66,15 @@ class LayerCache:
     """What one layer run sees of the cache: the tables of the layer whose cache it uses, and
     whether it may write them (`owns` is False for a layer that reads another layer's cache)."""
 
-    def __init__(self, manager, cache_layer: int, owns: bool):
+    def __init__(self, manager, cache_layer: int, owns: bool, prefix: str = ""):
         self.manager = manager
         self.layer = cache_layer
         self.owns = owns
+        self.prefix = prefix              # the name under which this part's states lie ("" for the layer's own)
+
+    def scoped(self, name: str) -> "LayerCache":
+        """The same cache as a part of the layer sees it whose needs were moved under `name` (`CacheNeeds.named`)."""
+        return LayerCache(self.manager, self.layer, self.owns, f"{self.prefix}.{name}" if self.prefix else name)
 
     @property
     def group(self) -> int:
@@ -79,7 +84,11 @@ class LayerCache:
         return self.manager.tables(self.layer)
 
     def state(self):
-        return self.manager.states[self.layer]
+        return self.manager.states[(self.layer, self.prefix) if self.prefix else self.layer]
+
+    def state_of(self, name: str):
+        """A further state table of this part, by name."""
+        return self.manager.states[(self.layer, f"{self.prefix}.{name}" if self.prefix else name)]
 
 
 class Part:

@@ -8,6 +8,10 @@
     outputs are normed: x += post_mixer(mixer(x)); x += post_ffn(ffn(x)); a layer may have no
     feed-forward.
 
+"parallel": one norm, and both branches read its output h: x += s1 * mixer(shift(h)) + s2 * ffn(h), with
+    an optional weight a channel on each branch and an optional token shift ahead of the mixer (the row
+    before a request's first row of a step is kept in the layer's state).
+
 The residual x is float32 and is updated in place. Each sum is one kernel together with the
 norm before it and the norm after it, when those are RMS norms.
 """
@@ -148,3 +152,79 @@ class PostNormBlock(Part):
             return x, h
         m = self.ffn.forward(h if narrow else x)
         return x, add_branch(self.ctx, x, m, self.norms["post_ffn"], next_norm, copy_out=narrow)
+
+
+class ParallelBlock(Part):
+    """x <- x + (s1 * mixer(shift(h)) + s2 * ffn(h)) with h = pre(x): one norm, two branches that read it.
+    The branches' weighted sum is one kernel (32-bit), the residual sum and the next layer's norm another."""
+
+    @classmethod
+    def expected_tensors(cls, spec):
+        from .registry import part_class
+
+        out = {}
+        out.update(part_class("mixer", spec.mixer.kind).expected_tensors(spec.mixer))
+        if spec.ffn is not None:
+            out.update(part_class("feed_forward", spec.ffn.kind).expected_tensors(spec.ffn))
+        n = spec.norms["pre"]
+        out.update(part_class("norm", n.kind).expected_tensors(n))
+        for name in (spec.scales or ()):
+            if name is not None:
+                out[name] = (n.width,)
+        if spec.shift is not None:
+            out[spec.shift] = (n.width,)
+        return out
+
+    def __init__(self, spec, ctx):
+        super().__init__(spec, ctx)
+        if "pre" not in spec.norms:
+            raise ValueError("parallel block: the norm `pre` is missing")
+        self.width = spec.norms["pre"].width
+        self.mixer = build_part("mixer", spec.mixer, ctx)
+        self.ffn = build_part("feed_forward", spec.ffn, ctx) if spec.ffn is not None else None
+        self.norm = build_part("norm", spec.norms["pre"], ctx)
+        if spec.scales is not None and (len(spec.scales) != 2 or spec.scales[0] is None or (spec.scales[1] is None) != (spec.ffn is None)):
+            raise ValueError(f"parallel block: branch weights {spec.scales} for a layer with{'out' if spec.ffn is None else ''} a feed-forward")
+
+    @property
+    def graph_safe(self) -> bool:
+        parts = [self.mixer, self.norm] + ([self.ffn] if self.ffn is not None else [])
+        return all(p.graph_safe for p in parts)
+
+    def cache_needs(self):
+        from ..cache import CacheNeeds, StateSpec
+
+        needs = self.mixer.cache_needs().named("mixer")
+        if self.spec.shift is not None:
+            needs = needs.merged(CacheNeeds(states=(("shift", StateSpec((self.width,))),)))
+        return needs
+
+    def first_norm(self):
+        return self.norm
+
+    def load(self, tensors):
+        import torch
+
+        self.mixer.load(tensors)
+        if self.ffn is not None:
+            self.ffn.load(tensors)
+        self.norm.load(tensors)
+        dev = self.ctx.device
+        f32 = lambda name: tensors[name].to(dev).float().contiguous()
+        one = lambda: torch.ones((self.width,), dtype=torch.float32, device=dev)
+        names = self.spec.scales or (None, None)
+        self.scale_mixer = f32(names[0]) if names[0] is not None else one()
+        self.scale_ffn = (f32(names[1]) if names[1] is not None else one()) if self.ffn is not None else None
+        self.shift = f32(self.spec.shift) if self.spec.shift is not None else None
+
+    def forward(self, x, h, batch, cache, next_norm):
+        if h is None:
+            h = self.norm.forward(x)
+        hm = h
+        if self.shift is not None:
+            hm = K.token_shift(h, self.shift, cache.state_of("shift"), batch.row_entry, batch.entry_ranges(), batch.slots, batch.entries,
+                               keep=cache.owns)
+        a = self.mixer.forward(hm, batch, cache.scoped("mixer"))
+        m = self.ffn.forward(h) if self.ffn is not None else None
+        both = K.weighted_sum2(a, self.scale_mixer, m, self.scale_ffn)
+        return x, add_branch(self.ctx, x, both, None, next_norm)

@@ -14,6 +14,11 @@ output uv_h (sum_j p_j c_j) is one more small product a head, which also applies
     q' = [uk_h^T q_plain | rot(q_rot)]  `head_linear` with the rotation of the tail
     y = attention(q', lines, sink)      the tensor-core kernel for such lines (bfloat16) or the row-wise kernel; the sink in the denominator
     o = (uv_h y) * sigmoid(g)           `head_linear` with the gate, then the output product
+
+A rotation of neighbouring components (2i, 2i+1) runs through the same kernels, which pair component i
+with i + rot/2: the rotated parts only ever meet in the dot product q_rot . k_rot, which does not change
+when both are reordered alike, so the rows of uq and dkv that make them are reordered once at load (the
+even components first, then the odd ones).
 """
 from __future__ import annotations
 
@@ -57,7 +62,16 @@ class LatentAttention(Part):
         H = s.num_heads
         names = [w["dq"], w["dkv"]] + ([w["g"]] if s.gated else [])
         self.w_down = stack_rows(ctx, tensors, names, "latent_attention")
-        self.w_uq = pad_columns(ctx, matrix_named(ctx, tensors, w["uq"]))           # the append kernel writes the latent this wide
+        w_uq = matrix_named(ctx, tensors, w["uq"])
+        if getattr(self.position, "neighbours", False):
+            r, d = s.rot_dim, s.head_dim
+            order = torch.cat([torch.arange(0, r, 2), torch.arange(1, r, 2)]).to(ctx.device)
+            at = s.q_rank + s.kv_rank
+            self.w_down[at : at + r] = self.w_down[at : at + r].index_select(0, order)
+            w_uq = w_uq.clone().view(H, d + r, -1)
+            w_uq[:, d:] = w_uq[:, d:].index_select(1, order)
+            w_uq = w_uq.view(H * (d + r), -1)
+        self.w_uq = pad_columns(ctx, w_uq)           # the append kernel writes the latent this wide
         self.w_o = pad_columns(ctx, matrix_named(ctx, tensors, w["o"]))
         dev = ctx.device
         # a matrix a head. In 32-bit [heads, in, out] for the FMA kernel: uk as it is stored (rows are a head's plain

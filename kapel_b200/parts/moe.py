@@ -10,6 +10,7 @@ with this feed-forward can be recorded. All experts' weights of a role are one t
 (down(act(gate h) * up h)) keep gate and up of an expert one below the other: the first grouped
 product gives gate|up a pair, the gated unit's kernel the second product's input. A shared expert (a
 feed-forward part of its own that every token runs) is added in the kernel that sums the experts up.
+The gated activation "clamped_swish" bounds both halves: min(gate, L) sigmoid(a min(gate, L)) (clamp(up, -L, L) + 1).
 """
 from __future__ import annotations
 
@@ -40,7 +41,10 @@ class MoE(Part):
 
     def __init__(self, spec, ctx):
         super().__init__(spec, ctx)
-        if spec.activation not in (K.ACT_CODES if spec.gated else K.MOE_ACT_CODES):
+        self.clamped = spec.gated and spec.activation == "clamped_swish"
+        if self.clamped and not (spec.limit is not None and spec.limit > 0):
+            raise ValueError(f"moe: the bounded gated unit needs a positive `limit`, got {spec.limit}")
+        if not self.clamped and spec.activation not in (K.ACT_CODES if spec.gated else K.MOE_ACT_CODES):
             raise ValueError(f"moe: activation {spec.activation!r} is not built" + (" for gated experts" if spec.gated else ""))
         if spec.scoring not in K.ROUTE_SCORING:
             raise ValueError(f"moe: scoring {spec.scoring!r} is not built")
@@ -76,7 +80,10 @@ class MoE(Part):
         also = self.shared.forward(h) if self.shared is not None else None
         if s.gated:
             both = K.moe_grouped(h, self.w_up, lists, "none", True, False, torch.float32)
-            inner = K.glu(both, s.activation, out_dtype=self.w_up.dtype)
+            if self.clamped:
+                inner = K.glu_clamped(both, s.limit, s.swish_alpha, out_dtype=self.w_up.dtype)
+            else:
+                inner = K.glu(both, s.activation, out_dtype=self.w_up.dtype)
         else:
             inner = K.moe_grouped(h, self.w_up, lists, s.activation, True, False, self.w_up.dtype)
         y = K.moe_grouped(inner, self.w_down, lists, "none", False, True, torch.float32)
