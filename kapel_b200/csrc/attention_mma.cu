@@ -58,6 +58,8 @@ struct AttMmaParams {
     int rows, hq, hkv, d, page_size, table_width, n_pages;
     int window, split, slots;
     int keep;                  // with a window: keys [0, keep) stay visible below it (prompt kernel only, one slot)
+    int block;                 // > 0: a row at position i sees only the keys from floor(i / block) * block on (prompt kernel only, one slot)
+    const float* sinks;        // [hq] or null: e^sink joins a row's denominator (prompt kernel only, one slot)
     int decode_bar_offset;     // bytes from the start of shared memory to the decode kernel's mbarriers
     int direct;                // 1: a row whose keys all lie in one slot was written to `out` by that slot's block
     int relative;              // 1: every request brings one token (tile t = row t = request t) and slots are counted from the row's first visible key, else from key 0
@@ -289,6 +291,7 @@ __device__ __forceinline__ AmTile am_tile_info(const AttMmaParams& p, int tile, 
     x.rows_valid = x.nq * x.group;
     x.c_first = p.row_count[x.row0];
     x.klo = (p.window > 0 && x.c_first > p.window) ? x.c_first - p.window : 0;
+    if (p.block > 0 && x.c_first > 0) x.klo = max(x.klo, (x.c_first - 1) / p.block * p.block);      // the first row's block starts first
     x.khi = x.c_first > 0 ? x.c_first + x.nq - 1 : 0;       // a padding row sees nothing
     if (p.split > 0) {
         // Counted from the window's start, a windowed row's keys fill whole slots: window / split of
@@ -523,6 +526,7 @@ attention_mma_kernel(const AttMmaParams p, const __grid_constant__ CUtensorMap m
         const bool own = r < rows_valid;
         cnt[h] = own ? x.c_first + r / group : 0x7fffffff;
         fst[h] = (own && p.window > 0 && cnt[h] > p.window) ? cnt[h] - p.window : 0;
+        if (own && p.block > 0 && cnt[h] > 0) fst[h] = max(fst[h], (cnt[h] - 1) / p.block * p.block);
     }
     const int fst_hi = __reduce_max_sync(0xffffffffu, max(fst[0], fst[1]));
     const int cnt_lo = __reduce_min_sync(0xffffffffu, min(cnt[0], cnt[1]));
@@ -558,7 +562,13 @@ attention_mma_kernel(const AttMmaParams p, const __grid_constant__ CUtensorMap m
         const int z1 = p.slots > 1 ? min(p.slots - 1, (cnt[h] - 1) / p.split) : 0;
         if (z0 == z1) {
             if (slot != z0) continue;
-            const float inv = l_run[h] > 0.f ? 1.f / l_run[h] : 0.f;
+            float inv = l_run[h] > 0.f ? 1.f / l_run[h] : 0.f;
+            if (p.sinks != nullptr) {                           // the weights were taken against the keys' maximum
+                const float sink = p.sinks[head];
+                const float top = fmaxf(m_run[h], sink);
+                const float wk = m_run[h] == -INFINITY ? 0.f : __expf(m_run[h] - top);
+                inv = wk / (l_run[h] * wk + __expf(sink - top));
+            }
             bf16* dst = p.out + ((size_t)row * p.hq + head) * d;
 #pragma unroll
             for (int i = 0; i < NT_O; ++i)
@@ -1337,11 +1347,12 @@ static int attention_mma_run(const AttMmaParams& p, int tiles, int decode, float
     return 0;
 }
 
-extern "C" int kb_attention_mma(void* out, const void* q, const void* k_table, const void* v_table,
+extern "C" int kb_attention_mma_masked(void* out, const void* q, const void* k_table, const void* v_table,
                                 const int* block_table, const int* row_count, const int* tile_entry,
                                 const int* tile_row0, const int* tile_nq, int tiles, int rows, int hq, int hkv, int d,
                                 int page_size, int table_width, int n_pages, int window, int split, int slots,
-                                float scale, float cap, int decode, int relative, int keep, float* scratch, void* stream) {
+                                float scale, float cap, int decode, int relative, int keep, float* scratch, int block,
+                                const float* sinks, void* stream) {
     // decode: 0 for prompt portions; else the most rows (tokens x query heads of a kv head) any tile
     // holds, at most 16.
     KB_REQUIRE(rows >= 0 && tiles >= 0 && hq > 0 && hkv > 0 && hq % hkv == 0, "attention_mma: rows %d, tiles %d, heads %d over %d", rows, tiles, hq, hkv);
@@ -1359,9 +1370,11 @@ extern "C" int kb_attention_mma(void* out, const void* q, const void* k_table, c
     KB_REQUIRE(hkv <= 65535, "attention_mma: %d kv heads is too many for one launch", hkv);
     KB_REQUIRE(keep >= 0 && (keep == 0 || (window > 0 && !decode && split == 0 && slots == 1)),
                "attention_mma: %d first keys kept need a window, prompt portions and one slot", keep);
+    KB_REQUIRE(block >= 0 && ((block == 0 && sinks == nullptr) || (!decode && split == 0 && slots == 1 && keep == 0)),
+               "attention_mma: a block mask (%d) or sinks need prompt portions, one slot and no kept first keys", block);
     if (rows == 0 || tiles == 0) return 0;
     AttMmaParams p;
-    p.keep = keep;
+    p.keep = keep; p.block = block; p.sinks = sinks;
     p.q = (const bf16*)q; p.k_table = (const bf16*)k_table; p.v_table = (const bf16*)v_table;
     p.block_table = block_table; p.row_count = row_count; p.tile_entry = tile_entry; p.tile_row0 = tile_row0;
     p.tile_nq = tile_nq; p.out = (bf16*)out; p.partial = slots > 1 ? scratch : nullptr;
@@ -1373,6 +1386,16 @@ extern "C" int kb_attention_mma(void* out, const void* q, const void* k_table, c
     p.qkv_parts = nullptr; p.qkv_stride = 0; p.qkv_splits = 0; p.stage_offset = 0; p.cos_sin = nullptr; p.lines = nullptr;
     p.k_new = p.v_new = nullptr; p.table_lines = 0;
     return attention_mma_run(p, tiles, decode, scratch, stream);
+}
+
+extern "C" int kb_attention_mma(void* out, const void* q, const void* k_table, const void* v_table,
+                                const int* block_table, const int* row_count, const int* tile_entry,
+                                const int* tile_row0, const int* tile_nq, int tiles, int rows, int hq, int hkv, int d,
+                                int page_size, int table_width, int n_pages, int window, int split, int slots,
+                                float scale, float cap, int decode, int relative, int keep, float* scratch, void* stream) {
+    return kb_attention_mma_masked(out, q, k_table, v_table, block_table, row_count, tile_entry, tile_row0, tile_nq, tiles, rows, hq, hkv, d,
+                                   page_size, table_width, n_pages, window, split, slots, scale, cap, decode, relative, keep, scratch, 0,
+                                   nullptr, stream);
 }
 
 // Whether kb_attention_decode_fused takes these sizes (else: kb_rope_append, then kb_attention_mma).
@@ -1405,7 +1428,7 @@ extern "C" int kb_attention_decode_fused(void* out, const float* qkv_parts, int 
     KB_REQUIRE(hkv <= 65535, "attention_decode_fused: %d kv heads is too many for one launch", hkv);
     if (rows == 0) return 0;
     AttMmaParams p;
-    p.keep = 0;
+    p.keep = 0; p.block = 0; p.sinks = nullptr;
     p.q = nullptr; p.k_table = (const bf16*)k_table; p.v_table = (const bf16*)v_table;
     p.block_table = block_table; p.row_count = row_count; p.tile_entry = nullptr; p.tile_row0 = nullptr;
     p.tile_nq = nullptr; p.out = (bf16*)out; p.partial = slots > 1 ? scratch : nullptr;

@@ -764,7 +764,8 @@ def paged_attention_decode_fused(qkv: "SplitSum", cos_sin, lines, k_table, v_tab
 
 def paged_attention_mma(q, k_table, v_table, block_table, row_count, tiles, page_size: int, window: Optional[int],
                         scale: float, softcap: Optional[float], decode: int, split: int, slots: int,
-                        relative: bool = False, pairs: Optional[int] = None, keep_first: int = 0) -> torch.Tensor:
+                        relative: bool = False, pairs: Optional[int] = None, keep_first: int = 0, block: int = 0,
+                        sinks: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Attention over the paged cache on tensor cores (bfloat16). `tiles` = (tile_entry, tile_row0,
     tile_nq) int32 device tensors: each tile is up to `attention_mma_rows(decode) // group` tokens of
     one request at consecutive positions. `decode` is 0 for prompt portions, else the most rows
@@ -772,8 +773,12 @@ def paged_attention_mma(q, k_table, v_table, block_table, row_count, tiles, page
     absolute multiples of it over `slots` blocks (slots >= ceil(longest count / split)). With
     `relative` (decode mode, every tile one token) the multiples are counted from each row's first
     visible key, so a windowed row needs ceil(window / split) slots however long its history. With a
-    window, `keep_first` keys from position 0 stay visible below it (prompt portions in one slot only)."""
+    window, `keep_first` keys from position 0 stay visible below it (prompt portions in one slot only).
+    With `block` > 0 a row at position i sees only the keys from floor(i / block) * block on, and with
+    `sinks` [hq] float32 e^sink joins each row's denominator (both: prompt portions in one slot only)."""
     rows, hq, d = q.shape
+    if sinks is not None:
+        _need(sinks, "attention sinks", torch.float32, (hq,))
     _need(q, "attention q", torch.bfloat16)
     _need(k_table, "attention k table", torch.bfloat16)
     _need(v_table, "attention v table", torch.bfloat16)
@@ -790,7 +795,7 @@ def paged_attention_mma(q, k_table, v_table, block_table, row_count, tiles, page
     lib = library()
     need = lib.kb_attention_mma_scratch_floats(rows, hq, d, int(slots))
     scratch = _fresh((need,), torch.float32, q.device) if need else None
-    if not decode and not keep_first and attention_prompt_kernel(hq, hkv, d, page_size, softcap) == "tcgen05":
+    if not decode and not keep_first and not block and sinks is None and attention_prompt_kernel(hq, hkv, d, page_size, softcap) == "tcgen05":
         _check(
             lib.kb_attention_tc(_ptr(out), _ptr(q), _ptr(k_table), _ptr(v_table), _ptr(block_table), _ptr(row_count),
                                 _ptr(tile_entry), _ptr(tile_row0), _ptr(tile_nq), n_tiles, rows, hq, hkv, d, int(page_size),
@@ -802,10 +807,11 @@ def paged_attention_mma(q, k_table, v_table, block_table, row_count, tiles, page
                                                 int(slots), _stream()))
         return out
     _check(
-        lib.kb_attention_mma(_ptr(out), _ptr(q), _ptr(k_table), _ptr(v_table), _ptr(block_table), _ptr(row_count),
-                             _ptr(tile_entry), _ptr(tile_row0), _ptr(tile_nq), n_tiles, rows, hq, hkv, d, int(page_size),
-                             int(block_table.shape[1]), int(n_pages), int(window or 0), int(split), int(slots), _f(scale),
-                             _f(softcap or 0.0), int(decode), int(bool(relative) and bool(decode)), int(keep_first or 0), _ptr(scratch), _stream())
+        lib.kb_attention_mma_masked(_ptr(out), _ptr(q), _ptr(k_table), _ptr(v_table), _ptr(block_table), _ptr(row_count),
+                                    _ptr(tile_entry), _ptr(tile_row0), _ptr(tile_nq), n_tiles, rows, hq, hkv, d, int(page_size),
+                                    int(block_table.shape[1]), int(n_pages), int(window or 0), int(split), int(slots), _f(scale),
+                                    _f(softcap or 0.0), int(decode), int(bool(relative) and bool(decode)), int(keep_first or 0),
+                                    _ptr(scratch), int(block or 0), _ptr(sinks), _stream())
     )
     return out
 

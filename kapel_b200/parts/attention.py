@@ -223,9 +223,20 @@ class Attention(Part):
         q = K.conv_append(stacked, 0, nq, self.qk_bias, self.conv, cache.state_of("conv"), batch.row_entry, batch.entry_ranges(),
                           batch.slots, batch.entries, group.lines, k_table, s.num_heads, s.num_kv_heads, s.head_dim, s.conv, cache.owns,
                           self.ctx.dtype)
-        y = K.paged_attention_rows(q.view(-1, s.num_heads, s.head_dim), k_table, k_table, group.block_table, batch.row_entry,
-                                   batch.row_count, self.ctx.page_size, None, s.scale, None, batch.attention_slots(s.block_mask or None),
-                                   sinks=self.sinks, block=s.block_mask)
+        q = q.view(-1, s.num_heads, s.head_dim)
+        heads_per_kv = s.num_heads // s.num_kv_heads
+        y = None
+        if s.head_dim % 16 == 0 and K.attention_mma_takes(q.dtype, s.head_dim, heads_per_kv):
+            # prompt portions go to the tensor-core kernel, which knows the block mask and the sink (in one slot: a row
+            # reads at most a block of keys); a pass of single tokens stays with the row-wise kernel below
+            decode, tiles, _, _, _ = batch.attention_tiles(heads_per_kv, s.num_kv_heads, None, s.head_dim, "mma", keep_first=0)
+            if not decode:
+                y = K.paged_attention_mma(q, k_table, k_table, group.block_table, batch.row_count, tiles, self.ctx.page_size, None,
+                                          s.scale, None, 0, 0, 1, False, block=s.block_mask, sinks=self.sinks)
+        if y is None:
+            y = K.paged_attention_rows(q, k_table, k_table, group.block_table, batch.row_entry, batch.row_count, self.ctx.page_size,
+                                       None, s.scale, None, batch.attention_slots(s.block_mask or None), sinks=self.sinks,
+                                       block=s.block_mask)
         y = y.view(y.shape[0], nq)
         width = product_width(self.ctx, nq)
         if width != nq:
