@@ -515,6 +515,10 @@ extern "C" long long kb_decay_scan_scratch_floats(int rows, int heads, int d, in
     return (long long)rows * heads * ((removal ? 5ll : 3ll) * d + e + 2);
 }
 
+// 0: the launcher chooses how many columns of the memory a warp of the scan holds; 1 or 2: that many (for tests and measurements).
+static int g_scan_columns = 0;
+extern "C" void kb_decay_scan_columns(int n) { g_scan_columns = (n == 1 || n == 2) ? n : 0; }
+
 static int run_decay_scan(float* out, const ScanInputs& in, float* state, int n_slots, const int* entry_start, const int* entry_end,
                           const int* slots, int entries, int heads, int d, int e, bool removal, cudaStream_t s) {
     ScanParams p;
@@ -527,7 +531,7 @@ static int run_decay_scan(float* out, const ScanInputs& in, float* state, int n_
     }
     // columns a warp: two where that still leaves about eight warps a multiprocessor
     const long long columns = (long long)entries * heads * e;
-    const int dw = columns / 2 >= 8ll * sms ? 2 : 1;
+    const int dw = g_scan_columns ? g_scan_columns : (columns / 2 >= 8ll * sms ? 2 : 1);
     KB_REQUIRE((e + SC * dw - 1) / (SC * dw) <= 65535 && heads <= 65535, "decay_scan: too many heads or value components for one launch");
     dim3 grid(entries, heads, (e + SC * dw - 1) / (SC * dw));
     const int need = (d + 31) / 32;

@@ -1071,8 +1071,9 @@ def token_shift(h: torch.Tensor, mu: torch.Tensor, state: torch.Tensor, row_entr
 
 def conv_state_floats(hq: int, hkv: int, d: int, taps: int) -> int:
     """Floats a request keeps between steps for the short convolutions on queries and keys: the last
-    taps - 1 inputs of every channel."""
-    return (taps - 1) * (hq + hkv) * d
+    taps - 1 inputs of every channel (one float that nobody reads where a filter has one weight, so that
+    the state table has a line a request all the same)."""
+    return max(1, (taps - 1) * (hq + hkv) * d)
 
 
 def conv_append(stacked, q_off: int, k_off: int, bias: Optional[torch.Tensor], conv: torch.Tensor, state: torch.Tensor, row_entry,
@@ -1108,6 +1109,12 @@ def conv_append(stacked, q_off: int, k_off: int, bias: Optional[torch.Tensor], c
         _ptr(slots), _ptr(lines if write_kv else None), int(entries), rows, int(hq), int(hkv), int(d), int(taps), int(bool(write_kv)),
         ctypes.c_longlong(table_lines), int(page_size), _stream()))
     return q
+
+
+def decay_scan_columns(n: int = 0) -> None:
+    """How many columns of a head's memory a warp of the decay scan holds: 1 or 2, or 0 for the
+    launcher's own choice by the warps a step has (for tests and measurements)."""
+    library().kb_decay_scan_columns(int(n))
 
 
 def gdelta_scan(stacked, r_off: int, k_off: int, v_off: int, a_off: int, w1_off: int, w2: torch.Tensor, w0: torch.Tensor,
