@@ -1,7 +1,7 @@
 """Throughput of the engine at Gemma 2 sizes with random weights, on one GPU.
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--size 2b|9b|27b] [--layers L] [--impl reference]
-    python bench.py --design fusitar|kofutar|teluzen [--design-sizes s,m]      (another line: see `design_line`)
+    python bench.py --design fusitar|kofutar|teluzen|lokedra [--design-sizes s,m]      (another line: see `design_line`)
 
 A "step" is one decode step. The default run has the layer sizes of the 2B configuration
 (26 layers, hidden 2304, 8 heads over 4 kv heads of 256, intermediate 9216, vocabulary 256000,
@@ -427,6 +427,30 @@ def teluzen_config(z):
             "layers": [{"type": "attention", "mixer": mixer, "mlp": dense if i == 0 else moe} for i in range(z["layers"])]}
 
 
+# --design lokedra: the Lokedra design (parallel blocks with a token shift; the generalized delta rule; chunked attention
+# behind short convolutions whose values are its keys, with 1 in the denominator, beside linear attention behind a forget
+# gate; attention through latents with stretched rotation; bounded gated experts) beside Kofutar, the engine's other design
+# with a delta rule and latent attention, and Fusitar, its other design with masked attention on the same kernels and
+# experts, at equal sizes: the same width, heads, head size, vocabulary, as many layers, experts of the same size. Its
+# layers take turns: parallel, delta, latent attention, delta; chunks as long as the others' window; latents as Kofutar's.
+LOKEDRA_LORA = 64
+
+
+def lokedra_config(z):
+    moe = {"kind": "moe", "expert": {"ff": z["ff"], "limit": 7.0}, "router": {"experts": z["experts"], "top": z["top"]}}
+    par = {"type": "parallel", "mlp": moe, "mixer": {
+        "left": {"heads": z["heads"], "kv_heads": z["kv_heads"], "dim": z["dim"], "vdim": z["dim"], "conv": 4, "scale": z["dim"] ** -0.5,
+                 "mask": {"size": z["window"]}},
+        "right": {"heads": z["heads"], "dim": z["dim"], "vdim": z["dim"]}, "left_scale": 1.0, "right_scale": 1.0}}
+    rec = {"type": "general_delta", "mlp": moe, "mixer": {"heads": z["heads"], "dim": z["dim"], "lora": LOKEDRA_LORA}}
+    lat = {"type": "latent_attention", "mlp": moe,
+           "mixer": {"heads": z["heads"], "dim": z["dim"], "rot_dim": 64, "vdim": z["dim"], "q_rank": z["width"] * 3 // 4, "kv_rank": KOFUTAR_KV_RANK,
+                     "scale": (z["dim"] + 64) ** -0.5,
+                     "rot": {"base": 10000.0, "dims": 64, "scaling": {"factor": 8.0, "original": 1024, "fast": 32.0, "slow": 1.0}}}}
+    return {"architecture": "Lokedra", "vocab": z["vocab"], "width": z["width"], "norm": {"eps": 1e-6}, "embedding": {"scale": z["width"] ** 0.5},
+            "layers": [(par, rec, lat, rec)[i % 4] for i in range(z["layers"])]}
+
+
 def gemma_config(z):
     return {"architectures": ["Gemma2ForCausalLM"], "model_type": "gemma2", "num_hidden_layers": z["layers"], "hidden_size": z["width"],
             "num_attention_heads": z["heads"], "num_key_value_heads": z["kv_heads"], "head_dim": z["dim"],
@@ -452,6 +476,23 @@ def design_kernel_rooflines(which, z, kind, rows, context, batch, pk):
         experts_read = min(z["experts"], batch * (z["top"] - 1)) + 1
         return {"attention": ("bytes", layers * batch * (min(context, win) * hkv * 2 * d * 2.0 + (max(0, context - win) // TELUZEN_POOL) * hkv * 2 * d * 4.0)),
                 "feed_forward": ("bytes", 2.0 * z["top"] * z["ff"] * w * 2 + moe_layers * experts_read * 3.0 * z["ff"] * w * 2)}
+    if which == "lokedra":
+        par_layers, lat_layers, rec_layers = (layers + 3) // 4, (layers + 1) // 4, layers // 2
+        r, kv = 64, KOFUTAR_KV_RANK
+        in_chunk = lambda c: (c - 1) % win + 1              # keys a query that has seen c positions reads: its chunk's so far
+        if kind == "prefill":
+            pairs = rows * (rows + 1) // 2
+            # the memories a row and head: the generalized delta rule decays, removes along the unit key and writes (5 a value of
+            # the [d, d] memory) and reads twice (4); the forget gate's memory decays and writes (3) and reads once (2)
+            return {"attention": ("flops", par_layers * 4.0 * sum(in_chunk(c) for c in range(1, rows + 1)) * hq * d),
+                    "latent_attention": ("flops", lat_layers * 2.0 * pairs * hq * (2 * d + r)),
+                    "feed_forward": ("flops", layers * 2.0 * rows * 3 * z["top"] * z["ff"] * w),
+                    "decay_scan": ("flops", (rec_layers * 9.0 + par_layers * 5.0) * rows * hq * d * d)}
+        experts_read = min(z["experts"], batch * z["top"])
+        return {"attention": ("bytes", par_layers * batch * in_chunk(context) * hkv * d * 2.0),          # a key is also the value: one line a position
+                "latent_attention": ("bytes", lat_layers * batch * context * (kv + r) * 2.0),
+                "feed_forward": ("bytes", layers * experts_read * 3.0 * z["ff"] * w * 2),
+                "decay_scan": ("bytes", (rec_layers + par_layers) * batch * hq * d * d * 4 * 2.0)}
     if which == "kofutar":
         att_layers, lat_layers, rec_layers = (layers + 3) // 4, (layers + 1) // 4, layers // 2
         r, kv, ff = 64, KOFUTAR_KV_RANK, z["top"] * z["ff"]
@@ -501,6 +542,17 @@ TELUZEN_KERNEL_CLASSES = {
 }
 
 
+# Lokedra's chunked attention runs the row-wise kernel (single tokens) and the mma.sync prompt kernel with the block mask, as
+# Fusitar's attention does; its latent layers the kernel over shared lines with the products a head around it; its experts
+# the grouped products with the bounded gated unit between them; its two memories the decay scan behind their own inputs' kernels.
+LOKEDRA_KERNEL_CLASSES = {
+    "attention": ("paged_attention_rows", "paged_attention_mma"),
+    "latent_attention": ("latent_attention_mma", "head_linear"),
+    "feed_forward": ("moe_grouped", "glu_clamped"),
+    "decay_scan": ("gdelta_scan", "gate_scan"),
+}
+
+
 def design_point(which, z, steps, warmup, clocks, pk):
     """Prefill of 2,048 tokens and decode at batch 8 for one design at one size: tokens a second through
     the engine (recorded passes), and the device time of each kernel entry point in one eager pass."""
@@ -510,7 +562,7 @@ def design_point(which, z, steps, warmup, clocks, pk):
     from kapel_b200 import kernels as K
     from kapel_b200.engine import Engine, StepEntry
 
-    cfg = {"fusitar": fusitar_config, "kofutar": kofutar_config, "gemma2": gemma_config, "teluzen": teluzen_config}[which](z)
+    cfg = {"fusitar": fusitar_config, "kofutar": kofutar_config, "gemma2": gemma_config, "teluzen": teluzen_config, "lokedra": lokedra_config}[which](z)
     room = (DESIGN_BATCH + 1) * (DESIGN_HISTORY + 4 * (steps + warmup) + 128) + PREFILL_TOKENS
     engine = Engine.random(cfg, seed=0, dtype="bfloat16", max_tokens=room, max_sequences=DESIGN_BATCH + 2)
     rng = np.random.default_rng(0)
@@ -555,7 +607,7 @@ def design_point(which, z, steps, warmup, clocks, pk):
         must = design_kernel_rooflines(which, z, kind, PREFILL_TOKENS, DESIGN_HISTORY, DESIGN_BATCH, pk)
         classes = {}
         for name, shape, calls, ms in rows:
-            for cls, members in {"kofutar": KOFUTAR_KERNEL_CLASSES, "teluzen": TELUZEN_KERNEL_CLASSES}.get(which, KERNEL_CLASSES).items():
+            for cls, members in {"kofutar": KOFUTAR_KERNEL_CLASSES, "teluzen": TELUZEN_KERNEL_CLASSES, "lokedra": LOKEDRA_KERNEL_CLASSES}.get(which, KERNEL_CLASSES).items():
                 if name in members:
                     classes[cls] = classes.get(cls, 0.0) + ms
         if which in ("gemma2", "kofutar"):   # the dense way down is a plain product: count the products whose inner width is the intermediate size
@@ -593,7 +645,7 @@ def design_line(args) -> int:
     sizes = {}
     for name in args.design_sizes.split(","):
         z = DESIGN_SIZES[name]
-        beside = ("gemma2",) if args.design == "fusitar" else ("fusitar", "gemma2")
+        beside = ("gemma2",) if args.design == "fusitar" else (("kofutar", "fusitar") if args.design == "lokedra" else ("fusitar", "gemma2"))
         if args.design_beside is not None:
             beside = tuple(b for b in args.design_beside.split(",") if b)
         sizes[name] = {"shape": z}
@@ -625,8 +677,8 @@ def main() -> int:
     ap.add_argument("--skip-check", action="store_true", help="leave out the check of the timed logits against the 32-bit path")
     ap.add_argument("--breakdown", action="store_true",
                     help="instead of the JSON line: device time by kernel for one prefill step and one eager decode step")
-    ap.add_argument("--design", default=None, choices=["fusitar", "kofutar", "teluzen"],
-                    help="instead of the default line: this design beside Gemma 2 (kofutar: beside Fusitar and Gemma 2) at equal sizes, prefill and decode, with each like kernel's roofline fraction")
+    ap.add_argument("--design", default=None, choices=["fusitar", "kofutar", "teluzen", "lokedra"],
+                    help="instead of the default line: this design beside Gemma 2 (kofutar and teluzen: beside Fusitar and Gemma 2; lokedra: beside Kofutar and Fusitar) at equal sizes, prefill and decode, with each like kernel's roofline fraction")
     ap.add_argument("--design-beside", default=None, help="which other designs run beside it (comma separated; empty: none); default: the closest ones")
     ap.add_argument("--design-sizes", default="s,m", help="which of the design sizes (s, m), comma separated")
     args = ap.parse_args()
