@@ -162,7 +162,7 @@ struct ScanInputs {
 
 struct GDeltaParams {
     int row_width, r_off, k_off, v_off, a_off, w1_off, lora;
-    const float* w2;            // [heads d, lora]
+    const float* w2;            // [lora, heads d]: the net's second layer turned, so that neighbouring threads read neighbouring weights
     const float* w0;            // [heads d]
     const float* a_bias;        // [heads d]
     float decay_scale;          // w = exp(-decay_scale * sigmoid(.))
@@ -170,50 +170,67 @@ struct GDeltaParams {
     int heads, d;
 };
 
-// One block a row. The small net's hidden layer tanh(w1 h) lies in shared memory; a thread a channel
-// computes its decay and removal rate, a warp a head the unit key and the two dot products.
-template <typename TS>
-__global__ void __launch_bounds__(256)
-gdelta_prep_kernel(const Src<TS> src, const GDeltaParams p, const ScanInputs s) {
-    extern __shared__ float sm[];                               // hidden [lora] | w [n] | a [n]
-    const int r = blockIdx.x;
-    const int n = p.heads * p.d;
-    float* hid = sm;
-    float* sw = hid + p.lora;
-    float* sa = sw + n;
-    const size_t base = (size_t)r * p.row_width;
-    for (int j = threadIdx.x; j < p.lora; j += blockDim.x) hid[j] = tanhf(src.at(base + p.w1_off + j));
+// One block RB rows. The small net's hidden layers tanh(w1 h) of the block's rows lie in shared memory; a thread a channel
+// reads its weights of the second layer once for all RB rows and leaves the decay and the removal rate in the scratch
+// (which the same block reads back below); a warp a (row, head) then makes the unit key and the two dot products.
+// RB is 8 for prompt portions (the second layer's weights cross from L2 once in eight rows) and 1 for a few rows.
+template <typename TS, int RB>
+__global__ void __launch_bounds__(1024)
+gdelta_prep_kernel(const Src<TS> src, const GDeltaParams p, const ScanInputs s, int rows) {
+    extern __shared__ float hid[];                              // [RB][lora]
+    const int r0 = blockIdx.x * RB;
+    const int nr = min(RB, rows - r0);
+    const int n = p.heads * p.d, d = p.d;
+    for (int idx = threadIdx.x; idx < RB * p.lora; idx += blockDim.x) {
+        const int rr = idx / p.lora, j = idx - rr * p.lora;
+        hid[idx] = rr < nr ? tanhf(src.at((size_t)(r0 + rr) * p.row_width + p.w1_off + j)) : 0.f;
+    }
     __syncthreads();
     for (int c = threadIdx.x; c < n; c += blockDim.x) {
-        float z = 0.f;
-        const float* w2 = p.w2 + (size_t)c * p.lora;
-        for (int j = 0; j < p.lora; ++j) z = fmaf(w2[j], hid[j], z);
-        sw[c] = expf(-p.decay_scale * rc_sigmoid(z + p.w0[c]));
-        sa[c] = rc_sigmoid(src.at(base + p.a_off + c) + p.a_bias[c]);
+        float z[RB];
+#pragma unroll
+        for (int rr = 0; rr < RB; ++rr) z[rr] = 0.f;
+        for (int j = 0; j < p.lora; ++j) {
+            const float wj = p.w2[(size_t)j * n + c];
+#pragma unroll
+            for (int rr = 0; rr < RB; ++rr) z[rr] = fmaf(wj, hid[rr * p.lora + j], z[rr]);
+        }
+        const float w0 = p.w0[c], ab = p.a_bias[c];
+        const int h = c / d, i = c - h * d;
+#pragma unroll
+        for (int rr = 0; rr < RB; ++rr) {
+            if (rr < nr) {
+                float* vec = s.vec + ((size_t)(r0 + rr) * p.heads + h) * 5 * d;
+                vec[d + i] = expf(-p.decay_scale * rc_sigmoid(z[rr] + w0));
+                vec[4 * d + i] = rc_sigmoid(src.at((size_t)(r0 + rr) * p.row_width + p.a_off + c) + ab);      // the rate; times the unit key below
+            }
+        }
     }
     __syncthreads();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, warps = blockDim.x >> 5;
-    for (int h = warp; h < p.heads; h += warps) {
+    for (int pair = warp; pair < nr * p.heads; pair += warps) {
+        const int rr = pair / p.heads, h = pair - rr * p.heads;
+        const int r = r0 + rr;
+        const size_t base = (size_t)r * p.row_width;
         float kk = 0.f;
-        for (int i = lane; i < p.d; i += 32) {
-            const float k = src.at(base + p.k_off + h * p.d + i);
+        for (int i = lane; i < d; i += 32) {
+            const float k = src.at(base + p.k_off + h * d + i);
             kk = fmaf(k, k, kk);
         }
         kk = warp_sum(kk);
         const float inv = 1.f / sqrtf(kk + p.unit_eps);
         float br = 0.f, kr = 0.f;
-        float* vec = s.vec + ((size_t)r * p.heads + h) * 5 * p.d;
-        for (int i = lane; i < p.d; i += 32) {
-            const int c = h * p.d + i;
-            const float k = src.at(base + p.k_off + c), rr = src.at(base + p.r_off + c);
-            const float u = k * inv, b = sa[c] * u, w = sw[c];
-            vec[i] = w * rr;
-            vec[p.d + i] = w;
-            vec[2 * p.d + i] = k;
-            vec[3 * p.d + i] = u;
-            vec[4 * p.d + i] = b;
-            br = fmaf(b, rr, br);
-            kr = fmaf(k, rr, kr);
+        float* vec = s.vec + ((size_t)r * p.heads + h) * 5 * d;
+        for (int i = lane; i < d; i += 32) {
+            const int c = h * d + i;
+            const float k = src.at(base + p.k_off + c), q = src.at(base + p.r_off + c);
+            const float u = k * inv, b = vec[4 * d + i] * u, w = vec[d + i];
+            vec[i] = w * q;
+            vec[2 * d + i] = k;
+            vec[3 * d + i] = u;
+            vec[4 * d + i] = b;
+            br = fmaf(b, q, br);
+            kr = fmaf(k, q, kr);
             s.val[(size_t)r * n + c] = src.at(base + p.v_off + c);
         }
         br = warp_sum(br);
@@ -288,8 +305,26 @@ __device__ __forceinline__ void scan_copy16(float* dst, const float* src) {
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(d32), "l"(src) : "memory");
 }
 
+// R values that lie together, by the widest loads that fit (shared memory, 16-byte aligned where R >= 4).
+template <int R>
+__device__ __forceinline__ void scan_load(float (&dst)[R], const float* p) {
+    if constexpr (R % 4 == 0) {
+#pragma unroll
+        for (int i = 0; i < R / 4; ++i) {
+            const float4 v = reinterpret_cast<const float4*>(p)[i];
+            dst[4 * i] = v.x; dst[4 * i + 1] = v.y; dst[4 * i + 2] = v.z; dst[4 * i + 3] = v.w;
+        }
+    } else if constexpr (R == 2) {
+        const float2 v = *reinterpret_cast<const float2*>(p);
+        dst[0] = v.x; dst[1] = v.y;
+    } else {
+#pragma unroll
+        for (int i = 0; i < R; ++i) dst[i] = p[i];
+    }
+}
+
 // One block = one request of the step x one head x SC * DW columns of the memory; a warp DW columns, lane l
-// the rows l, l + 32, ... of them in registers. R: rows a lane holds; CH: rows of the step staged at a time
+// the rows R l .. R l + R - 1 of them in registers (a row's vectors then come from shared memory 16 bytes a load). R: rows a lane holds; CH: rows of the step staged at a time
 // (asynchronous copies, the next chunk while this one is walked); REMOVAL: whether u and b exist.
 template <int R, int CH, int DW, bool REMOVAL>
 __global__ void __launch_bounds__(SC * 32)
@@ -317,7 +352,7 @@ decay_scan_kernel(const ScanParams p) {
 #pragma unroll
     for (int ci = 0; ci < DW; ++ci)
 #pragma unroll
-        for (int i = 0; i < R; ++i) S[ci][i] = (c0 + ci < e && lane + 32 * i < d) ? st[(size_t)(c0 + ci) * d + lane + 32 * i] : 0.f;
+        for (int i = 0; i < R; ++i) S[ci][i] = (c0 + ci < e && lane * R + i < d) ? st[(size_t)(c0 + ci) * d + lane * R + i] : 0.f;
 
     const bool wide = d % 4 == 0 && ((uintptr_t)p.vec & 15) == 0;
     auto stage = [&](int chunk, int buf) {
@@ -375,28 +410,28 @@ decay_scan_kernel(const ScanParams p) {
         for (int t = 0; t < nr; ++t) {
             const float* in = rows + (size_t)t * rowf;
             const float br = in[tail + COLS], kr = in[tail + COLS + 1];
-            float wr[R], w[R], k[R];
-#pragma unroll
-            for (int i = 0; i < R; ++i) {
-                wr[i] = in[lane + 32 * i];
-                w[i] = in[DP + lane + 32 * i];
-                k[i] = in[2 * DP + lane + 32 * i];
+            float wr[R], w[R], k[R], u[REMOVAL ? R : 1], b[REMOVAL ? R : 1];
+            scan_load<R>(wr, in + lane * R);
+            scan_load<R>(w, in + DP + lane * R);
+            scan_load<R>(k, in + 2 * DP + lane * R);
+            if constexpr (REMOVAL) {
+                scan_load<R>(u, in + 3 * DP + lane * R);
+                scan_load<R>(b, in + 4 * DP + lane * R);
             }
 #pragma unroll
             for (int ci = 0; ci < DW; ++ci) {
                 const float v = in[tail + warp * DW + ci];
                 float o;
                 if constexpr (REMOVAL) {
-                    float u[R], b[R];
                     float xp = 0.f, xq = 0.f;
 #pragma unroll
                     for (int i = 0; i < R; ++i) {
-                        u[i] = in[3 * DP + lane + 32 * i];
-                        b[i] = in[4 * DP + lane + 32 * i];
                         xp = fmaf(S[ci][i], u[i], xp);
                         xq = fmaf(S[ci][i], wr[i], xq);
                     }
-                    // two sums over 32 lanes: the halves swap one of them, then both are reduced side by side
+                    // two sums over 32 lanes: the halves swap one of them, then both are reduced side by side (the lower lanes
+                    // end with p, the upper with q). Two broadcasts then give every lane both; one exchange between the halves
+                    // and a choice a lane instead measured a fifth slower (1.23 against 1.03 ms at 2,048 rows, 16 heads of 128).
                     float y = (hi16 ? xq : xp) + __shfl_xor_sync(0xffffffffu, hi16 ? xp : xq, 16);
                     y += __shfl_xor_sync(0xffffffffu, y, 8);
                     y += __shfl_xor_sync(0xffffffffu, y, 4);
@@ -425,7 +460,7 @@ decay_scan_kernel(const ScanParams p) {
     for (int ci = 0; ci < DW; ++ci)
 #pragma unroll
         for (int i = 0; i < R; ++i)
-            if (c0 + ci < e && lane + 32 * i < d) st[(size_t)(c0 + ci) * d + lane + 32 * i] = S[ci][i];
+            if (c0 + ci < e && lane * R + i < d) st[(size_t)(c0 + ci) * d + lane * R + i] = S[ci][i];
 }
 
 // ------------------------------------------------------------------------------------------ two branches with a weight a channel
@@ -517,7 +552,7 @@ extern "C" long long kb_decay_scan_scratch_floats(int rows, int heads, int d, in
 
 // 0: the launcher chooses how many columns of the memory a warp of the scan holds; 1 or 2: that many (for tests and measurements).
 static int g_scan_columns = 0;
-extern "C" void kb_decay_scan_columns(int n) { g_scan_columns = (n == 1 || n == 2) ? n : 0; }
+extern "C" void kb_decay_scan_columns(int n) { g_scan_columns = (n == 1 || n == 2 || n == 4) ? n : 0; }
 
 static int run_decay_scan(float* out, const ScanInputs& in, float* state, int n_slots, const int* entry_start, const int* entry_end,
                           const int* slots, int entries, int heads, int d, int e, bool removal, cudaStream_t s) {
@@ -529,9 +564,10 @@ static int run_decay_scan(float* out, const ScanInputs& in, float* state, int n_
         int dev = 0;
         if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
     }
-    // columns a warp: two where that still leaves about eight warps a multiprocessor
+    // columns a warp: the most that still leaves about four warps a multiprocessor (a warp reads a row's vectors once for all
+    // its columns, and walks them as independent chains)
     const long long columns = (long long)entries * heads * e;
-    const int dw = g_scan_columns ? g_scan_columns : (columns / 2 >= 8ll * sms ? 2 : 1);
+    int dw = g_scan_columns ? g_scan_columns : (columns / 4 >= 4ll * sms ? 4 : (columns / 2 >= 4ll * sms ? 2 : 1));
     KB_REQUIRE((e + SC * dw - 1) / (SC * dw) <= 65535 && heads <= 65535, "decay_scan: too many heads or value components for one launch");
     dim3 grid(entries, heads, (e + SC * dw - 1) / (SC * dw));
     const int need = (d + 31) / 32;
@@ -544,17 +580,25 @@ static int run_decay_scan(float* out, const ScanInputs& in, float* state, int n_
 #define KB_SCAN_W(R, CH)                                  \
     do {                                                  \
         if (removal) {                                    \
-            if (dw == 2) KB_SCAN(R, CH, 2, true);         \
+            if (dw == 4) KB_SCAN(R, CH, (R <= 4 ? 4 : 2), true);      \
+            else if (dw == 2) KB_SCAN(R, CH, 2, true);    \
             else KB_SCAN(R, CH, 1, true);                 \
         } else {                                          \
-            if (dw == 2) KB_SCAN(R, CH, 2, false);        \
+            if (dw == 4) KB_SCAN(R, CH, (R <= 4 ? 4 : 2), false);     \
+            else if (dw == 2) KB_SCAN(R, CH, 2, false);   \
             else KB_SCAN(R, CH, 1, false);                \
         }                                                 \
     } while (0)
     if (need <= 1) KB_SCAN_W(1, 16);
     else if (need <= 2) KB_SCAN_W(2, 16);
     else if (need <= 4) KB_SCAN_W(4, 8);
-    else KB_SCAN_W(SCAN_R, 4);
+    else {                                                  // eight rows a lane: at most two columns a warp fit the registers
+        if (dw == 4) {
+            dw = 2;
+            grid.z = (e + SC * dw - 1) / (SC * dw);
+        }
+        KB_SCAN_W(SCAN_R, 4);
+    }
 #undef KB_SCAN_W
 #undef KB_SCAN
     return check_launch("decay_scan");
@@ -583,8 +627,9 @@ extern "C" int kb_gdelta_scan(float* out, float* scratch, const void* src, int i
                    v_off + n <= row_width && a_off >= 0 && a_off + n <= row_width && w1_off >= 0 && w1_off + lora <= row_width,
                "gdelta: columns r %d, k %d, v %d, a %d, w1 %d (+%d) do not fit a row of %d", r_off, k_off, v_off, a_off, w1_off, lora, row_width);
     KB_REQUIRE(out && scratch && w2 && w0 && a_bias, "gdelta: weights or scratch are missing");
-    const size_t smem = (size_t)(lora + 2 * n) * sizeof(float);
-    KB_REQUIRE(smem <= 200 * 1024, "gdelta: %lld channels do not fit the shared memory of a block", n);
+    const bool few = rows <= DEPENDENT_ROWS;
+    const size_t smem = (size_t)(few ? 1 : 8) * lora * sizeof(float);
+    KB_REQUIRE(smem <= 200 * 1024, "gdelta: a decay net of %d hidden values does not fit the shared memory of a block", lora);
     if (entries == 0 || rows == 0) return 0;
     GDeltaParams g;
     g.row_width = row_width; g.r_off = r_off; g.k_off = k_off; g.v_off = v_off; g.a_off = a_off; g.w1_off = w1_off; g.lora = lora;
@@ -597,8 +642,13 @@ extern "C" int kb_gdelta_scan(float* out, float* scratch, const void* src, int i
     cudaStream_t s = (cudaStream_t)stream;
 #define KB_GD(TS)                                                                                                          \
     do {                                                                                                                   \
-        if (smem > 48 * 1024) cudaFuncSetAttribute(gdelta_prep_kernel<TS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
-        gdelta_prep_kernel<TS><<<rows, 256, smem, s>>>(Src<TS>{(const TS*)src, splits, (size_t)split_stride}, g, in);      \
+        if (few) {                                                                                                         \
+            if (smem > 48 * 1024) cudaFuncSetAttribute(gdelta_prep_kernel<TS, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+            gdelta_prep_kernel<TS, 1><<<rows, 1024, smem, s>>>(Src<TS>{(const TS*)src, splits, (size_t)split_stride}, g, in, rows); /* few rows: a channel or two a thread */ \
+        } else {                                                                                                           \
+            if (smem > 48 * 1024) cudaFuncSetAttribute(gdelta_prep_kernel<TS, 8>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+            gdelta_prep_kernel<TS, 8><<<(rows + 7) / 8, 512, smem, s>>>(Src<TS>{(const TS*)src, splits, (size_t)split_stride}, g, in, rows); \
+        }                                                                                                                  \
     } while (0)
     if (in_dt == KB_DT_F32) KB_GD(float);
     else if (in_dt == KB_DT_BF16) KB_GD(bf16);

@@ -1112,7 +1112,7 @@ def conv_append(stacked, q_off: int, k_off: int, bias: Optional[torch.Tensor], c
 
 
 def decay_scan_columns(n: int = 0) -> None:
-    """How many columns of a head's memory a warp of the decay scan holds: 1 or 2, or 0 for the
+    """How many columns of a head's memory a warp of the decay scan holds: 1, 2 or 4, or 0 for the
     launcher's own choice by the warps a step has (for tests and measurements)."""
     library().kb_decay_scan_columns(int(n))
 
@@ -1123,15 +1123,16 @@ def gdelta_scan(stacked, r_off: int, k_off: int, v_off: int, a_off: int, w1_off:
     """The generalized delta rule's read-out [rows, heads, d] (float32, not yet normed) over the rows of a
     step, request by request in row order, from and into `state` [slots, heads, d, d]. Per head, with the
     decay w = exp(-decay_scale sigmoid(w2 tanh(w1 h) + w0)), the removal rate a = sigmoid(a h + a_bias) and
-    the unit key u = k / sqrt(sum k^2 + unit_eps): S <- diag(w) S - (a u)(u^T S) + k v^T, o = S^T r. The
+    the unit key u = k / sqrt(sum k^2 + unit_eps): S <- diag(w) S - (a u)(u^T S) + k v^T, o = S^T r. `w2` is
+    the net's second layer turned, [hidden, heads d] (neighbouring threads read neighbouring weights). The
     columns r_off, k_off, v_off, a_off (heads d each) and w1_off (the small net's hidden layer, before
     its tanh) of `stacked` hold the projections."""
     src, dt, splits, stride, rows, width = _stacked(stacked, "gdelta input")
     n = heads * d
     _need(w2, "gdelta decay weights", torch.float32)
-    if w2.dim() != 2 or w2.shape[0] != n:
-        raise KernelError(f"gdelta: decay weights of {tuple(w2.shape)}, expected [{n}, hidden]")
-    lora = int(w2.shape[1])
+    if w2.dim() != 2 or w2.shape[1] != n:
+        raise KernelError(f"gdelta: decay weights of {tuple(w2.shape)}, expected [hidden, {n}] (the net's second layer, turned)")
+    lora = int(w2.shape[0])
     _need(w0, "gdelta decay bias", torch.float32, (n,))
     _need(a_bias, "gdelta removal bias", torch.float32, (n,))
     _need(state, "gdelta state", torch.float32)

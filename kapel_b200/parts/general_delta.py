@@ -41,7 +41,7 @@ class GeneralDelta(Part):
         self.w_o = pad_columns(self.ctx, matrix_named(self.ctx, tensors, w["o"]))      # the gate kernel writes rows this wide
         dev = self.ctx.device
         f32 = lambda n: tensors[n].to(dev).float().contiguous()
-        self.w2, self.w0, self.a_bias = f32(w["w2"]), f32(w["w0"]), f32(w["a_bias"])
+        self.w2, self.w0, self.a_bias = f32(w["w2"]).t().contiguous(), f32(w["w0"]), f32(w["a_bias"])      # the second layer turned: [lora, heads d]
         n = tensors[w["norm"]].to(dev)
         self.norm_weight = n.float().contiguous() if self.ctx.is_f32 else n.contiguous()
 

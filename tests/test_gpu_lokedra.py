@@ -366,7 +366,7 @@ def delta_case(rng, T, H, d, lora):
     return x
 
 
-@pytest.mark.parametrize("scan_columns", [0, 1, 2], indirect=True)
+@pytest.mark.parametrize("scan_columns", [0, 1, 2, 4], indirect=True)
 @pytest.mark.parametrize("H,d,lora", [(3, 16, 8), (1, 24, 3), (2, 40, 5), (2, 130, 20), (4, 64, 16)])
 def test_generalized_delta_rule_in_portions_and_token_by_token_against_plain(H, d, lora, scan_columns):
     """Three requests of unequal length: whole, then in portions down to two tokens beside each other's single tokens,
@@ -392,7 +392,7 @@ def test_generalized_delta_rule_in_portions_and_token_by_token_against_plain(H, 
         if len(rows) <= 4:
             rows = split_sum(rows)
         entry, ranges, slots = batch_of(step)
-        out = K.gdelta_scan(rows, 0, n, 2 * n, 4 * n, 5 * n, dev(w2), dev(w0), dev(ab), scale, 1e-6, state, ranges, slots, len(step), H, d).cpu().numpy()
+        out = K.gdelta_scan(rows, 0, n, 2 * n, 4 * n, 5 * n, dev(w2.T), dev(w0), dev(ab), scale, 1e-6, state, ranges, slots, len(step), H, d).cpu().numpy()
         at = 0
         for m, _, a, b in step:
             err = float(np.abs(out[at : at + b - a] - want[m][a:b]).max() / np.abs(want[m]).max())
@@ -402,12 +402,12 @@ def test_generalized_delta_rule_in_portions_and_token_by_token_against_plain(H, 
     walk(run, state, LENGTHS)
     before = state.clone()
     entry = dev([0, 1, 2, 3], torch.int32)
-    out = K.gdelta_scan(dev(data["a"][:4]), 0, n, 2 * n, 4 * n, 5 * n, dev(w2), dev(w0), dev(ab), scale, 1e-6, state, K.entry_ranges(entry, 4),
+    out = K.gdelta_scan(dev(data["a"][:4]), 0, n, 2 * n, 4 * n, 5 * n, dev(w2.T), dev(w0), dev(ab), scale, 1e-6, state, K.entry_ranges(entry, 4),
                         dev([0, 0, 0, 0], torch.int32), 4, H, d)
     assert float(out.abs().max()) == 0.0 and torch.equal(before, state)
 
 
-@pytest.mark.parametrize("scan_columns", [0, 1, 2], indirect=True)
+@pytest.mark.parametrize("scan_columns", [0, 1, 2, 4], indirect=True)
 @pytest.mark.parametrize("H,d,e", [(2, 24, 8), (1, 8, 40), (3, 40, 16), (2, 130, 5), (4, 48, 64)])
 def test_forget_gate_memory_in_portions_and_token_by_token_against_plain(H, d, e, scan_columns):
     from kapel_b200 import kernels as K
