@@ -172,7 +172,7 @@ def _read_mixer(kind: str, m: dict, where: str):
         if vdim != dim:
             raise ConfigError(f"config.json: `{w}left.vdim` = {vdim} must equal `{w}left.dim` = {dim}: the values are the keys")
         mask = _record(left, "mask", f"{w}left.")
-        chunked = LokedraChunked(heads, kv_heads, dim, vdim, _int(fl, [f"{w}left.conv"], hi=8),
+        chunked = LokedraChunked(heads, kv_heads, dim, vdim, _int(fl, [f"{w}left.conv"], hi=16),
                                  _float(fl, [f"{w}left.scale"], required=True),
                                  _int(_flat(mask, f"{w}left.mask."), [f"{w}left.mask.size"], hi=1 << 30))
         gdim = _int(fr, [f"{w}right.dim"], hi=_MAX_HEAD_DIM)

@@ -64,7 +64,7 @@ __global__ void keep_last_kernel(float* __restrict__ state, const T* __restrict_
 }
 
 // ------------------------------------------------------------------------------------------ convolutions ahead of attention
-constexpr int CONV_MAX_TAPS = 8;
+constexpr int CONV_MAX_TAPS = 16;
 
 struct ConvParams {
     int row_width, q_off, k_off, nq, nk;      // columns of the stacked product; nq = hq d, nk = hkv d

@@ -82,9 +82,9 @@ class Attention(Part):
         self.convolved = bool(spec.conv or spec.values_are_keys or spec.block_mask or spec.unit_sink or spec.qk_bias or spec.out_bias)
         self.out_bias = None
         if self.convolved:
-            if not (spec.values_are_keys and 1 <= spec.conv <= 8):
+            if not (spec.values_are_keys and 1 <= spec.conv <= 16):
                 raise ValueError("attention: a block mask, 1 in the denominator or biases on q, k and o are built for the path with "
-                                 f"convolutions (1 to 8 rows, got {spec.conv}) whose values are its keys")
+                                 f"convolutions (1 to 16 rows, got {spec.conv}) whose values are its keys")
             if (self.by_head or spec.gated or spec.q_norm or spec.k_norm or spec.keep_first or spec.softcap or spec.window or spec.bias
                     or spec.pool or spec.head_temp or spec.talk or spec.value_mix or spec.v_head_dim not in (None, spec.head_dim)):
                 raise ValueError("attention: convolutions together with norms, a gate, a window, a soft cap, pooled blocks, mixed heads or "
