@@ -13,7 +13,7 @@ weight a channel on each branch and a token shift ahead of the mixer. `type`:
 * "parallel": two mixers side by side, {left, right, left_scale, right_scale}: `left` is grouped-query
   attention behind short convolutions {heads, kv_heads, dim, vdim, conv, scale, mask{size}} whose values
   are its keys, over chunks of `mask.size` positions, with 1 in the softmax's denominator; `right`
-  {heads, dim, vdim} is linear attention whose forget gate also decides what is written.
+  {heads, dim, vdim} is gated linear attention whose input gate is one minus its forget gate.
 
 `mlp` is {kind: "moe", router{experts, top}, expert{ff, limit}} or null. `loop` {start, stop, times}: the
 layers start .. stop-1 run `times` times in a row with the same weights and a cache of their own each
@@ -170,7 +170,7 @@ def _read_mixer(kind: str, m: dict, where: str):
         dim = _int(fl, [f"{w}left.dim"], hi=_MAX_HEAD_DIM)
         vdim = _int(fl, [f"{w}left.vdim"], dim, hi=_MAX_HEAD_DIM)
         if vdim != dim:
-            raise ConfigError(f"config.json: `{w}left.vdim` = {vdim} must equal `{w}left.dim` = {dim}: the values are the keys")
+            raise ConfigError(f"config.json: `{w}left.vdim` = {vdim} must equal `{w}left.dim` = {dim}: this attention has no value projection, it reads its keys")
         mask = _record(left, "mask", f"{w}left.")
         chunked = LokedraChunked(heads, kv_heads, dim, vdim, _int(fl, [f"{w}left.conv"], hi=16),
                                  _float(fl, [f"{w}left.scale"], required=True),

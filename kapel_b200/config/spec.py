@@ -200,7 +200,7 @@ class GeneralDeltaSpec:
 
 @dataclass(frozen=True)
 class ForgetGateSpec:
-    """Linear attention whose forget gate also decides what is written (HGRN2): a matrix memory
+    """Gated linear attention with tied gates, the input gate being one minus the forget gate (HGRN2): a matrix memory
     S [head_dim, v_head_dim] a head and request.
 
     q = silu(q h) [heads, head_dim], v = v h [heads, v_head_dim], f = l + (1 - l) sigmoid(f h + f_bias)

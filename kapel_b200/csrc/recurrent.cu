@@ -14,7 +14,7 @@
 //                    Written on the old memory: with p = u^T S and q = (w r)^T S, o = q - p (b.r) + v (k.r),
 //                    so both dot products of a row are reduced together. `gdelta_prep` (the generalized
 //                    delta rule: decay through a small two-layer net, removal rate, unit keys) and
-//                    `gate_prep` (a forget gate with a lower bound that also decides what is written:
+//                    `gate_prep` (tied gates: a forget gate with a lower bound, and one minus it as the input gate:
 //                    w = f, k = 1 - f, no removal) make its inputs.
 //  weighted_sum2     out = a * va + b * vb + vc with a weight a channel on each branch.
 //

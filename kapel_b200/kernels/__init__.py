@@ -1151,8 +1151,8 @@ def gdelta_scan(stacked, r_off: int, k_off: int, v_off: int, a_off: int, w1_off:
 
 def gate_scan(stacked, q_off: int, f_off: int, v_off: int, f_bias: torch.Tensor, lower: torch.Tensor, state: torch.Tensor, ranges,
               slots, entries: int, heads: int, d: int, e: int) -> torch.Tensor:
-    """The read-out [rows, heads, e] (float32, not yet normed) of a matrix memory behind a forget gate that
-    also decides what is written: q = silu(.), f = lower + (1 - lower) sigmoid(. + f_bias) per head and
+    """The read-out [rows, heads, e] (float32, not yet normed) of a matrix memory with tied gates (the
+    input gate is one minus the forget gate): q = silu(.), f = lower + (1 - lower) sigmoid(. + f_bias) per head and
     channel; S <- diag(f) S + (1 - f) v^T, o = S^T q; `state` [slots, heads e d]."""
     src, dt, splits, stride, rows, width = _stacked(stacked, "gate_scan input")
     _need(f_bias, "gate_scan gate bias", torch.float32, (heads * d,))

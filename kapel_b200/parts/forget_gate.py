@@ -1,4 +1,4 @@
-"""Linear attention whose forget gate also decides what is written (HGRN2), as a mixer with a state
+"""Gated linear attention with tied gates, the input gate being one minus the forget gate (HGRN2), as a mixer with a state
 of its own.
 
 One stacked product gives q | f | v in 32-bit. The scan's kernels apply silu to q, make the gate

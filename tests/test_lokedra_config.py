@@ -71,7 +71,7 @@ def test_tensor_names_shapes_and_the_size_only_a_tensor_gives():
 @pytest.mark.parametrize("edit,words", [
     (lambda r: r["layers"][0].update(type="conv"), "type"),
     (lambda r: r["layers"][1]["mixer"]["left"].update(kv_heads=3), "multiple"),
-    (lambda r: r["layers"][1]["mixer"]["left"].update(vdim=6), "values are the keys"),
+    (lambda r: r["layers"][1]["mixer"]["left"].update(vdim=6), "no value projection"),
     (lambda r: r["layers"][1]["mixer"]["left"].pop("mask"), "mask"),
     (lambda r: r["layers"][1]["mixer"]["left"].update(conv=0), "conv"),
     (lambda r: r["layers"][1]["mixer"].pop("right"), "right"),
